@@ -6,6 +6,8 @@ needs: `KVSpec` (keys and values in pages; all of them, or a window) or
 KVSpec form a group that shares page ids and has a pool of its own:
 
     pool[group]   [layers of the group, pages, 2 (k, v), kv heads, page_size, head_dim]
+                  (values of another size than the keys: [layers, pages, kv heads * page_size * (head_dim + v_dim)],
+                  a page's keys [kv heads, page_size, head_dim] followed by its values [kv heads, page_size, v_dim])
     state[cache]  [max_requests, *shape]     one row per request slot
 
 A request holds one slot from open() to close(); its state rows are zeroed
@@ -23,10 +25,12 @@ from .pages import CacheError, OutOfPages, PageGroup, PageTables, UNMAPPED  # no
 
 @dataclass(frozen=True)
 class KVSpec:
-    """Keys and values of `num_kv_heads` heads of `head_dim`; window = 0 keeps every position."""
+    """Keys and values of `num_kv_heads` heads of `head_dim`; window = 0 keeps every position; v_dim = 0: values of
+    the keys' size, else their own size (a page then holds the keys of its slots followed by the values)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    v_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -61,6 +65,7 @@ class CacheManager:
             if isinstance(spec, KVSpec):
                 by_spec.setdefault(spec, []).append(cid)
         self.groups = [PageGroup(tuple(ids), s.num_kv_heads, s.head_dim, s.window) for s, ids in by_spec.items()]
+        self._v_dims = [s.v_dim or s.head_dim for s in by_spec]
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.groups)
         self.tables = PageTables(self.groups, page_size, list(num_pages), max_requests)
@@ -69,8 +74,9 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             pool = None
             if allocate:
-                pool = torch.zeros((len(grp.cache_ids), self.tables.pools[g].num_pages, 2, grp.num_kv_heads, page_size,
-                                    grp.head_dim), dtype=dtype, device=self.device)
+                shape = ((2, grp.num_kv_heads, page_size, grp.head_dim) if self._v_dims[g] == grp.head_dim
+                         else (grp.num_kv_heads * page_size * (grp.head_dim + self._v_dims[g]),))
+                pool = torch.zeros((len(grp.cache_ids), self.tables.pools[g].num_pages, *shape), dtype=dtype, device=self.device)
             self.pools.append(pool)
             for i, cid in enumerate(grp.cache_ids):
                 self.views[cid].group = g
@@ -83,7 +89,7 @@ class CacheManager:
     def bytes_per_token(self) -> int:
         """Cache bytes one position takes over all groups (every layer, keys and values)."""
         size = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.cache_ids) * 2 * g.num_kv_heads * g.head_dim * size for g in self.groups)
+        return sum(len(g.cache_ids) * g.num_kv_heads * (g.head_dim + vd) * size for g, vd in zip(self.groups, self._v_dims))
 
     def token_capacity(self) -> int:
         """Positions the smallest pool can hold."""

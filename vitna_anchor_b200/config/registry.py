@@ -1,6 +1,6 @@
 """One registry from an architecture's name to what builds it.
 
-config.json's `architectures[0]` chooses the entry (the reference compares
+config.json's `architectures[0]` (or the plain string `architecture`) chooses the entry (the reference compares
 `model_type` instead, engine/src/model.c:61-75; that key is the fallback here).
 An entry gives: how to read the typed configuration, the manifest of tensors,
 how to build the model from host tensors, and which tensors random
@@ -38,7 +38,7 @@ def architectures() -> List[str]:
 
 
 def resolve(config_json: Mapping[str, Any]) -> Architecture:
-    names = config_json.get("architectures") or []
+    names = config_json.get("architectures") or config_json.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for n in names:
@@ -58,3 +58,7 @@ def _register_builtin() -> None:
     from .llama import LlamaConfig
     register_architecture(Architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_manifest, build_llama,
                                        is_norm_weight, model_types=("llama",)), replace=True)
+    from ..models import lupanex as _lx
+    from .lupanex import ARCHITECTURE, LupanexConfig
+    register_architecture(Architecture(ARCHITECTURE, LupanexConfig.from_dict, _lx.lupanex_manifest, _lx.build_lupanex,
+                                       _lx.is_norm_weight), replace=True)

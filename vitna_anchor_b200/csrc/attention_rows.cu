@@ -14,6 +14,11 @@
 // boundaries are multiples of 128 in absolute position, so the order of the
 // sums of a (request, position) does not depend on how the tokens were cut
 // into steps or on what else is in the batch.
+//
+// Two things beyond the plain form, both optional: values of another size than the keys (vd != hd; a page then
+// holds [nkv][page_size][hd] keys followed by [nkv][page_size][vd] values, which for vd == hd is the usual
+// [2][nkv][page_size][hd]), and a bias that depends on the distance between query and key, added to the scaled
+// score: dist_bias [max_dist][nh] float32, row min(pos - key, max_dist - 1).
 #include "common.cuh"
 
 namespace vk {
@@ -25,20 +30,21 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
-    T* __restrict__ out, int nh, int nkv, int hd, int page_size, int max_blocks, float scale, int window) {
+    T* __restrict__ out, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, float scale, int window,
+    const float* __restrict__ dist_bias, int max_dist) {
     extern __shared__ float smem[];
     float* qs = smem;                         // [hd]
     float* pr = qs + hd;                      // [128]
     float* scratch = pr + ATT_THREADS;        // [32]
-    __shared__ size_t row_off[ATT_THREADS];   // element offset of each key's K row in the layer's cache
+    __shared__ size_t row_off[ATT_THREADS];   // element offset of each key's row of values in the layer's cache
 
     const int t = tok_list ? tok_list[blockIdx.x] : blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int kvh = h / (nh / nkv);
     const int pos = positions[t];
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
-    const size_t page_stride = (size_t)2 * nkv * page_size * hd;
-    const size_t v_off = (size_t)nkv * page_size * hd;
+    const size_t page_stride = (size_t)nkv * page_size * (hd + vd);
+    const size_t v_base = (size_t)nkv * page_size * hd;     // where a page's values begin
 
     const T* qrow = q + ((size_t)t * nh + h) * hd;
     for (int d = tid; d < hd; d += ATT_THREADS) qs[d] = to_f32<T>(qrow[d]);
@@ -53,12 +59,16 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
         float s = -INFINITY;
         if (valid) {
             const int page = bt[key / page_size];
-            const size_t off = (size_t)page * page_stride + ((size_t)kvh * page_size + key % page_size) * hd;
-            row_off[tid] = off;
-            const T* kr = cache + off;
+            const size_t in_page = (size_t)kvh * page_size + key % page_size;
+            row_off[tid] = (size_t)page * page_stride + v_base + in_page * vd;      // the key's row of values
+            const T* kr = cache + (size_t)page * page_stride + in_page * hd;
             float dot = 0.0f;
             for (int d = 0; d < hd; d++) dot = fmaf(qs[d], to_f32<T>(kr[d]), dot);
             s = dot * scale;
+            if (dist_bias) {
+                const int n = pos - key;
+                s += dist_bias[(size_t)(n < max_dist ? n : max_dist - 1) * nh + h];
+            }
         }
         const float cmax = block_max(s, scratch);
         const float m_new = fmaxf(m, cmax);
@@ -73,20 +83,20 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
 #pragma unroll
         for (int a = 0; a < ATT_MAX_ACC; a++) {
             const int d = tid + a * ATT_THREADS;
-            if (d < hd) {
+            if (d < vd) {
                 float v = acc[a] * corr;
-                for (int j = j0; j <= j1; j++) v = fmaf(pr[j], to_f32<T>(cache[row_off[j] + v_off + d]), v);
+                for (int j = j0; j <= j1; j++) v = fmaf(pr[j], to_f32<T>(cache[row_off[j] + d]), v);
                 acc[a] = v;
             }
         }
         __syncthreads();  // pr and row_off are rewritten by the next run
     }
     const float inv = 1.0f / l;
-    T* orow = out + ((size_t)t * nh + h) * hd;
+    T* orow = out + ((size_t)t * nh + h) * vd;
 #pragma unroll
     for (int a = 0; a < ATT_MAX_ACC; a++) {
         const int d = tid + a * ATT_THREADS;
-        if (d < hd) orow[d] = from_f32<T>(acc[a] * inv);
+        if (d < vd) orow[d] = from_f32<T>(acc[a] * inv);
     }
 }
 
@@ -94,24 +104,36 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_rows_kernel(
 
 using namespace vk;
 
-// q, out [tokens, nh*hd]; cache: one layer [pages][2][nkv][page_size][hd];
+// q [tokens, nh*hd], out [tokens, nh*vd]; cache: one layer [pages][ nkv*page_size*hd keys | nkv*page_size*vd values ];
 // block_tables [segments, max_blocks]; token_seg, positions [all tokens]; tok_list [tokens] names the
-// tokens to run (null: 0..tokens-1).
-VK_API int vk_attention_rows(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
-                             const int32_t* positions, const int32_t* tok_list, void* out, int tokens, int nh, int nkv, int hd, int page_size,
-                             int max_blocks, float scale, int window, int dtype, cudaStream_t stream) {
+// tokens to run (null: 0..tokens-1); dist_bias [max_dist][nh] float32 or null.
+VK_API int vk_attention_rows_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
+                                    const int32_t* positions, const int32_t* tok_list, void* out, int tokens, int nh, int nkv, int hd, int vd,
+                                    int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist, int dtype,
+                                    cudaStream_t stream) {
     if (tokens <= 0) return VK_OK;
-    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
-    if (hd > ATT_THREADS * ATT_MAX_ACC || nh > 65535) return VK_TOO_LARGE;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || vd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
+    if (dist_bias && max_dist <= 0) return VK_BAD_SHAPE;
+    if (vd > ATT_THREADS * ATT_MAX_ACC || nh > 65535) return VK_TOO_LARGE;
     const size_t smem = (size_t)(hd + ATT_THREADS + 32) * sizeof(float);
+    if (smem > 48 * 1024) return VK_TOO_LARGE;
     dim3 grid(tokens, nh);
     if (dtype == 0)
         attention_rows_kernel<float><<<grid, ATT_THREADS, smem, stream>>>((const float*)q, (const float*)cache, block_tables,
-                                                                          token_seg, positions, tok_list, (float*)out, nh, nkv, hd,
-                                                                          page_size, max_blocks, scale, window);
+                                                                          token_seg, positions, tok_list, (float*)out, nh, nkv, hd, vd,
+                                                                          page_size, max_blocks, scale, window, dist_bias, max_dist);
     else
         attention_rows_kernel<__nv_bfloat16><<<grid, ATT_THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_tables, token_seg, positions, tok_list, (__nv_bfloat16*)out, nh,
-            nkv, hd, page_size, max_blocks, scale, window);
+            nkv, hd, vd, page_size, max_blocks, scale, window, dist_bias, max_dist);
     return launch_status();
+}
+
+// The plain form: values of the keys' size, no bias.
+VK_API int vk_attention_rows(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
+                             const int32_t* positions, const int32_t* tok_list, void* out, int tokens, int nh, int nkv, int hd, int page_size,
+                             int max_blocks, float scale, int window, int dtype, cudaStream_t stream) {
+    if (hd > ATT_THREADS * ATT_MAX_ACC) return VK_TOO_LARGE;
+    return vk_attention_rows_biased(q, cache, block_tables, token_seg, positions, tok_list, out, tokens, nh, nkv, hd, hd, page_size, max_blocks,
+                                    scale, window, nullptr, 0, dtype, stream);
 }

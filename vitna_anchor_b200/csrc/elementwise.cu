@@ -155,6 +155,50 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, const int32_t* __re
     }
 }
 
+// The attention mixer's step between its projections and the attention, in the form without a rotation: every q
+// head and k head is divided by its root mean square (eps inside the root; eps < 0: left as it is), q is then
+// multiplied by a factor that grows with the position,  1 + coef * ln(floor((pos + 1) / every) + 1)  (coef 0: none);
+// q goes to q_out, k and v into the token's cache slot.  Values may have another size than keys: a page is
+// [nkv][page_size][hd] keys followed by [nkv][page_size][vd] values.
+//
+// qkv [tokens, nh*hd + nkv*hd + nkv*vd]; q_out [tokens, nh*hd]; slot [tokens] or null; cache one layer or null.
+// A warp per head.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_norm_store_kernel(const T* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                                            const int32_t* __restrict__ slot, T* __restrict__ q_out, T* __restrict__ cache,
+                                                            int nh, int nkv, int hd, int vd, int page_size, float eps, float coef, int every) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const T* in = qkv + (size_t)t * ((size_t)(nh + nkv) * hd + (size_t)nkv * vd);
+    const int s = (slot && cache) ? slot[t] : -1;
+    const size_t page_stride = (size_t)nkv * page_size * (hd + vd);
+    T* kbase = s >= 0 ? cache + (size_t)(s / page_size) * page_stride : nullptr;
+    T* vbase = s >= 0 ? kbase + (size_t)nkv * page_size * hd : nullptr;
+    const int off = s >= 0 ? s % page_size : 0;
+    float factor = 1.0f;
+    if (coef != 0.0f) factor = 1.0f + coef * logf((float)((positions[t] + 1) / every) + 1.0f);
+    for (int h = warp; h < nh + nkv; h += nwarps) {
+        const T* v = in + (size_t)h * hd;
+        float inv = 1.0f;
+        if (eps >= 0.0f) {
+            float ss = 0.0f;
+            for (int d = lane; d < hd; d += 32) { const float x = to_f32<T>(v[d]); ss = fmaf(x, x, ss); }
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+        if (h < nh) {
+            T* dst = q_out + ((size_t)t * nh + h) * hd;
+            for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>((to_f32<T>(v[d]) * inv) * factor);
+        } else if (s >= 0) {
+            T* dst = kbase + ((size_t)(h - nh) * page_size + off) * hd;
+            for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(to_f32<T>(v[d]) * inv);
+        }
+    }
+    if (s >= 0) {
+        const T* vin = in + (size_t)(nh + nkv) * hd;
+        for (int u = threadIdx.x; u < nkv * vd; u += blockDim.x) vbase[((size_t)(u / vd) * page_size + off) * vd + u % vd] = vin[u];
+    }
+}
+
 // act_i = (g_i / (1 + exp(-g_i))) * u_i       (engine/src/ops.c:283-288)
 // gu [tokens, 2*inter]: gate columns, then up columns.
 template <typename T>
@@ -233,6 +277,19 @@ VK_API int vk_rope_store(const void* qkv, const int32_t* positions, const float*
         rope_store_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)qkv, positions, cos_t, sin_t, slot,
                                                                       (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, nh, nkv, hd,
                                                                       rot, page_size);
+    return launch_status();
+}
+
+VK_API int vk_qk_norm_store(const void* qkv, const int32_t* positions, const int32_t* slot, void* q_out, void* cache, int tokens, int nh,
+                            int nkv, int hd, int vd, int page_size, float eps, float coef, int every, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (nh <= 0 || nkv <= 0 || hd <= 0 || vd <= 0 || page_size <= 0 || (coef != 0.0f && every <= 0)) return VK_BAD_SHAPE;
+    if (dtype == 0)
+        qk_norm_store_kernel<float><<<tokens, 256, 0, stream>>>((const float*)qkv, positions, slot, (float*)q_out, (float*)cache, nh, nkv, hd,
+                                                                 vd, page_size, eps, coef, every);
+    else
+        qk_norm_store_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)qkv, positions, slot, (__nv_bfloat16*)q_out,
+                                                                         (__nv_bfloat16*)cache, nh, nkv, hd, vd, page_size, eps, coef, every);
     return launch_status();
 }
 

@@ -53,10 +53,14 @@ def random_model_on_device(config_json: Mapping[str, Any], seed: int, dtype="bfl
     for w in arch.manifest(cfg):
         if w.optional:
             continue
-        if arch.is_norm_weight(w.name):
-            weights[w.name] = torch.ones(w.shape, dtype=torch.float32, device=device)
+        shape = tuple(w.free_size if d is None else d for d in w.shape)
+        kind = arch.is_norm_weight(w.name)
+        if kind == "identity":
+            weights[w.name] = torch.eye(shape[0], dtype=torch.float32, device=device)
+        elif kind:
+            weights[w.name] = torch.ones(shape, dtype=torch.float32, device=device)
         else:
-            t = torch.empty(w.shape, dtype=torch.float32 if len(w.shape) < 2 else torch.bfloat16, device=device)
+            t = torch.empty(shape, dtype=torch.float32 if len(shape) < 2 else torch.bfloat16, device=device)
             t.normal_(0.0, std, generator=gen)
             weights[w.name] = t
     return arch.build(cfg, weights, compute_dtype(dtype), device)

@@ -28,7 +28,10 @@ class LayerRun:
 class DecoderModel:
     def __init__(self, *, embedding: TokenInput, blocks: Sequence[Block], schedule: Sequence[LayerRun], final_norm: Norm,
                  lm_head: LogitsOutput, position: Optional[PositionEncoding], dtype: torch.dtype, vocab_size: int,
-                 max_positions: int, config=None):
+                 max_positions: int, config=None, collect: Optional[Part] = None):
+        # collect: for a residual stream of another form than one float32 row a token (several rows joined by
+        # hyper-connections): collect.forward(x, ctx) -> float32 [T, hidden], run once after the last block
+        self.collect = collect
         self.embedding, self.blocks, self.schedule = embedding, list(blocks), list(schedule)
         self.final_norm, self.lm_head, self.position = final_norm, lm_head, position
         self.dtype, self.vocab_size, self.max_positions, self.config = dtype, vocab_size, max_positions, config
@@ -50,7 +53,7 @@ class DecoderModel:
         return list(self._cache_specs)
 
     def parts(self) -> List[Part]:
-        return [self.embedding, *self.blocks, self.final_norm, self.lm_head]
+        return [self.embedding, *self.blocks, self.final_norm, self.lm_head] + ([self.collect] if self.collect is not None else [])
 
     def step_weight_bytes(self) -> int:
         """Bytes of weights a decode step reads: every block as often as it runs, the output matrix once,
@@ -78,6 +81,8 @@ class DecoderModel:
             self.blocks[run.block].forward(x, ctx, cache, run.write_cache)
             if ctx.after_run is not None:
                 ctx.after_run(i)
+        if self.collect is not None:
+            x = self.collect.forward(x, ctx)
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
         if self.lm_head.fuses_norm(self.final_norm, ctx, logit_rows.shape[0]):

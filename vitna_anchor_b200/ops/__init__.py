@@ -656,3 +656,175 @@ def attention(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor
     if ctx.num_dec and not dec_ok:
         attention_rows(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, scale, window, ctx.dec_tokens)
     return out
+
+
+# ---------------------------------------------------------------------------
+# Residual streams, scaled embedding with learned positions, activations
+# ---------------------------------------------------------------------------
+
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, kind: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = act(x) element by element (in place unless out is given); kind: gelu (the erf form), gelu_tanh, silu."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    out = x if out is None else out
+    _req(x, "x"); _req(out, "out", x.dtype)
+    if out.numel() != x.numel():
+        raise KernelError("activation: sizes differ")
+    _check(lib().vk_activation(_p(x), _p(out), ctypes.c_size_t(x.numel()), ACTIVATIONS[kind], _dt(x), _stream()), "activation")
+    return out
+
+
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, pos_table: Optional[torch.Tensor], scale: float,
+                 out: torch.Tensor, copies: int = 1) -> torch.Tensor:
+    """out[t, j, :] = scale * table[ids[t]] + pos_table[positions[t]] for every copy j; out float32 [T, copies * width]."""
+    _req(table, "table", dims=2); _req(ids, "ids", torch.int32, 1); _req(positions, "positions", torch.int32, 1)
+    _req(out, "out", torch.float32, 2)
+    V, W = table.shape
+    if pos_table is not None:
+        _req(pos_table, "pos_table", torch.float32, 2)
+        if pos_table.shape[1] != W:
+            raise KernelError("embed_scaled: the position table's width differs")
+    if out.shape != (ids.shape[0], copies * W) or positions.shape[0] < ids.shape[0]:
+        raise KernelError("embed_scaled: out is not [tokens, copies * width]")
+    _check(lib().vk_embed_scaled(_p(table), _p(ids), _p(positions), _p(pos_table), ctypes.c_float(scale), _p(out), ids.shape[0], W, V,
+                                 0 if pos_table is None else pos_table.shape[0], copies, _dt(table), _stream()), "embed_scaled")
+    return out
+
+
+def hyper_step(xs: torch.Tensor, y: Optional[torch.Tensor], streams: int, *, mix: Optional[torch.Tensor] = None,
+               out_w: Optional[torch.Tensor] = None, in_w: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+               eps: float = 0.0, xn: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None) -> None:
+    """What lies between two sublayers of a model with `streams` residual rows a token (xs float32 [T, streams * W]):
+    with mix [streams, streams] (from, to) and out_w [streams] the rows become  x_j <- sum_i mix[i, j] x_i + out_w[j] y;
+    then  u = sum_i in_w[i] x_i  (all ones without in_w), written to sum_out (float32) and, normed with norm_w and eps,
+    to xn (compute dtype).  y (float32 [T, W]) is left zeroed."""
+    _req(xs, "xs", torch.float32, 2)
+    T, W = xs.shape[0], xs.shape[1] // streams
+    if xs.shape[1] != streams * W:
+        raise KernelError("hyper_step: xs is not [tokens, streams * width]")
+    for name, t, shape in (("y", y, (T, W)), ("mix", mix, (streams, streams)), ("out_w", out_w, (streams,)), ("in_w", in_w, (streams,)),
+                           ("norm_w", norm_w, (W,)), ("sum_out", sum_out, (T, W))):
+        if t is not None:
+            _req(t, name, torch.float32)
+            if tuple(t.shape) != shape:
+                raise KernelError(f"hyper_step: {name} is {tuple(t.shape)}, expected {shape}")
+    if xn is not None:
+        _req(xn, "xn", dims=2)
+        if tuple(xn.shape) != (T, W):
+            raise KernelError("hyper_step: xn is not [tokens, width]")
+    _check(lib().vk_hyper_step(_p(xs), _p(y), _p(mix), _p(out_w), _p(in_w), _p(norm_w), ctypes.c_float(eps), _p(xn), _p(sum_out), T, streams,
+                               W, 0 if xn is None else _dt(xn), _stream()), "hyper_step")
+
+
+# ---------------------------------------------------------------------------
+# Attention without a rotation: unit-RMS q and k, a query factor that grows with the position, a bias by distance
+# ---------------------------------------------------------------------------
+
+def kv_page_elems(nkv: int, page_size: int, hd: int, vd: int) -> int:
+    """Elements of one page of one layer: [nkv][page_size][hd] keys, then [nkv][page_size][vd] values."""
+    return nkv * page_size * (hd + vd)
+
+
+def _page_size_of(cache_layer: torch.Tensor, nkv: int, hd: int, vd: int) -> int:
+    per_page = cache_layer[0].numel()
+    ps = per_page // (nkv * (hd + vd))
+    if ps < 1 or ps * nkv * (hd + vd) != per_page or not cache_layer.is_contiguous():
+        raise KernelError("the cache layer is not [pages][nkv * page_size * (hd + vd)]")
+    return ps
+
+
+def qk_norm_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor,
+                  cache_layer: Optional[torch.Tensor], nh: int, nkv: int, hd: int, vd: int, page_size: int, *, eps: float = -1.0,
+                  q_coef: float = 0.0, q_every: int = 1) -> torch.Tensor:
+    """q and k heads divided by their root mean square (eps < 0: not), q times 1 + q_coef * ln(floor((pos + 1) / q_every) + 1);
+    q to q_out, k and v into the layer's pages at slot_mapping (-1: no write)."""
+    _req(qkv, "qkv", dims=2); _req(positions, "positions", torch.int32, 1); _req(q_out, "q_out", qkv.dtype, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + nkv) * hd + nkv * vd or q_out.shape != (T, nh * hd) or positions.shape[0] < T:
+        raise KernelError("qk_norm_store: shapes do not fit the head counts")
+    if cache_layer is not None:
+        _req(cache_layer, "cache_layer", qkv.dtype); _req(slot_mapping, "slot_mapping", torch.int32, 1)
+        if _page_size_of(cache_layer, nkv, hd, vd) != page_size or slot_mapping.shape[0] < T:
+            raise KernelError("qk_norm_store: the cache layer does not fit the page size")
+    _check(lib().vk_qk_norm_store(_p(qkv), _p(positions), _p(slot_mapping if cache_layer is not None else None), _p(q_out), _p(cache_layer),
+                                  T, nh, nkv, hd, vd, page_size, ctypes.c_float(eps), ctypes.c_float(q_coef), int(q_every), _dt(qkv),
+                                  _stream()), "qk_norm_store")
+    return q_out
+
+
+def attention_rows_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
+                          positions: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float,
+                          window: int = 0, dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of every token (or of those in tok_list) over its request's pages, any sizes, float32 arithmetic,
+    with values of size vd and, if given, dist_bias [distances, nh] (float32) added to the scaled scores by min(distance, last row)."""
+    _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
+    T = q.shape[0]
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+        raise KernelError("attention_rows_biased: shapes do not fit the head counts")
+    if token_seg.shape[0] != T or positions.shape[0] != T:
+        raise KernelError("attention_rows_biased: per-token arrays differ in length")
+    if dist_bias is not None:
+        _req(dist_bias, "dist_bias", torch.float32, 2)
+        if dist_bias.shape[1] != nh:
+            raise KernelError("attention_rows_biased: the bias table is not [distances, heads]")
+    n = T
+    if tok_list is not None:
+        _req(tok_list, "tok_list", torch.int32, 1)
+        n = tok_list.shape[0]
+    _check(lib().vk_attention_rows_biased(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out), n, nh,
+                                          nkv, hd, vd, page_size, block_tables.shape[1], ctypes.c_float(scale), window, _p(dist_bias),
+                                          0 if dist_bias is None else dist_bias.shape[0], _dt(q), _stream()), "attention_rows_biased")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# The gated delta rule
+# ---------------------------------------------------------------------------
+
+def delta_state_floats(G: int, H: int, dk: int, dv: int, taps: int) -> int:
+    """Floats of one request's state in one layer: the transposed matrix state of every head, then the last taps-1
+    inputs of the short convolution."""
+    return H * dv * dk + max(0, taps - 1) * (2 * G * dk + H * dv)
+
+
+def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float,
+               token_seg: torch.Tensor, seg_starts: torch.Tensor, seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor,
+               o: torch.Tensor, out: torch.Tensor, G: int, H: int, dk: int, dv: int, taps: int) -> torch.Tensor:
+    """The gated delta rule on a batch of segments, from the projections to the input of the output projection.
+    proj float32 [T, 2 G dk + 2 H dv + 2 H] = q | k | v | gate | b | a;  conv_w float32 [2 G dk + H dv, taps];  a_log, dt_bias [H];
+    norm_w [dv];  state float32 [slots, delta_state_floats];  prep [T, 2 G dk + H dv + 2 H] and o [T, H dv] float32 scratch;
+    out [T, H dv] in the compute dtype.  Three launches: prepare, recurrence (which also writes the state), gate."""
+    C = 2 * G * dk + H * dv
+    _req(proj, "proj", torch.float32, 2); _req(conv_w, "conv_w", torch.float32, 2); _req(a_log, "a_log", torch.float32, 1)
+    _req(dt_bias, "dt_bias", torch.float32, 1); _req(norm_w, "norm_w", torch.float32, 1); _req(state, "state", torch.float32, 2)
+    _req(prep, "prep", torch.float32, 2); _req(o, "o", torch.float32, 2); _req(out, "out", dims=2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(seg_starts, "seg_starts", torch.int32, 1); _req(seg_slots, "seg_slots", torch.int32, 1)
+    T, S = proj.shape[0], seg_slots.shape[0]
+    if (proj.shape[1] != C + H * dv + 2 * H or conv_w.shape != (C, taps) or a_log.shape[0] != H or dt_bias.shape[0] != H
+            or norm_w.shape[0] != dv or prep.shape != (T, C + 2 * H) or o.shape != (T, H * dv) or out.shape != (T, H * dv)
+            or state.shape[1] != delta_state_floats(G, H, dk, dv, taps) or token_seg.shape[0] != T or seg_starts.shape[0] != S + 1):
+        raise KernelError("delta_rule: shapes do not fit the head counts")
+    stride = ctypes.c_size_t(state.stride(0))
+    _check(lib().vk_delta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
+                                  _p(prep), T, G, H, dk, dv, taps, _stream()), "delta_prepare")
+    _check(lib().vk_delta_recurrence(_p(prep), _p(proj), _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, G, H, dk, dv, taps,
+                                     _stream()), "delta_recurrence")
+    _check(lib().vk_delta_gate(_p(o), _p(proj), _p(norm_w), ctypes.c_float(eps), _p(out), T, G, H, dk, dv, _dt(out), _stream()), "delta_gate")
+    return out
+
+
+def attention_biased(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int,
+                     page_size: int, scale: float, window: int = 0, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of a mixed batch over the paged cache in the unrotated form (values of their own size, a bias by
+    distance); `meta` is the page group's GroupMeta."""
+    return attention_rows_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size, scale,
+                                 window, dist_bias)
+
+
+def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x @ w.T) in x's dtype; kind one of ACTIVATIONS."""
+    return activation(linear(x, w, out, LINEAR_SAME), kind)

@@ -11,17 +11,22 @@ from .base import Block, FeedForward, Mixer, Norm, StepContext
 
 
 class PreNormBlock(Block):
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm] = None, ffn: Optional[FeedForward] = None):
+        """A layer without a feed-forward is the mixer's half alone."""
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 
     def tensors(self):
-        return self.mixer_norm.tensors() + self.mixer.tensors() + self.ffn_norm.tensors() + self.ffn.tensors()
+        return [t for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None for t in p.tensors()]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCacheView], write_cache: bool = True) -> None:
         if self.mixer.fuses_norm(self.mixer_norm, ctx):
             self.mixer.forward(x, ctx, cache, x, write_cache, norm=self.mixer_norm)
         else:
             self.mixer.forward(self.mixer_norm.forward(x, ctx, "block.xn"), ctx, cache, x, write_cache)
+        if self.ffn is None:
+            return
         if self.ffn.fuses_norm(self.ffn_norm, ctx):
             self.ffn.forward(x, ctx, x, norm=self.ffn_norm)
         else:

@@ -28,6 +28,29 @@ class Embedding(TokenInput):
         return ops.embed_rows(self.table, ctx.tokens, x)
 
 
+class ScaledEmbedding(TokenInput):
+    """x = scale * the token's row + a learned row for the token's position (unscaled), written `copies` times side by
+    side: float32 [T, copies * hidden], the form a model with several residual streams starts from."""
+
+    def __init__(self, vocab: int, hidden: int, table: torch.Tensor, scale: float = 1.0, positions: Optional[torch.Tensor] = None,
+                 copies: int = 1):
+        if table.shape != (vocab, hidden) or (positions is not None and (positions.dim() != 2 or positions.shape[1] != hidden)):
+            raise ValueError("the embedding tables do not fit the sizes")
+        self.vocab, self.hidden, self.scale, self.copies = vocab, hidden, float(scale), int(copies)
+        self.table = table.contiguous()
+        self.positions = None if positions is None else positions.to(torch.float32).contiguous()
+
+    def tensors(self):
+        return [self.table] + ([] if self.positions is None else [self.positions])
+
+    def weight_bytes(self) -> int:
+        return 0                     # a row per token is read, not the tables
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        x = ctx.workspace.rows("x", ctx.num_tokens, self.copies * self.hidden, torch.float32)
+        return ops.embed_scaled(self.table, ctx.tokens, ctx.positions, self.positions, self.scale, x, self.copies)
+
+
 class LMHead(LogitsOutput):
     def __init__(self, vocab: int, hidden: int, weight: torch.Tensor):
         if weight.shape != (vocab, hidden):

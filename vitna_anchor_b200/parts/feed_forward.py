@@ -1,6 +1,8 @@
 """SwiGLU feed-forward: y = W_down (silu(W_gate xn) * (W_up xn)), added into the residual stream
 (engine/src/model.c:962-972; silu(g) = g / (1 + exp(-g)), engine/src/ops.c:283-288).
-The gate and up matrices are stacked by rows so that one product reads xn once."""
+The gate and up matrices are stacked by rows so that one product reads xn once.
+
+The dense feed-forward: y = W_down act(W_up xn), act one of ops.ACTIVATIONS (the erf or the tanh form of gelu, silu)."""
 from __future__ import annotations
 
 import torch
@@ -40,4 +42,21 @@ class SwiGLU(FeedForward):
         else:
             gu = ops.linear(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), ops.LINEAR_SAME)
             act = ops.silu_mul(gu, act_buf)
+        ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)
+
+
+class DenseMLP(FeedForward):
+    def __init__(self, hidden: int, intermediate: int, w_up: torch.Tensor, w_down: torch.Tensor, activation: str = "gelu"):
+        if w_up.shape != (intermediate, hidden) or w_down.shape != (hidden, intermediate):
+            raise ValueError("feed-forward weights do not fit the sizes")
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.hidden, self.intermediate, self.activation = hidden, intermediate, activation
+        self.w_up, self.w_down = w_up.contiguous(), w_down.contiguous()
+
+    def tensors(self):
+        return [self.w_up, self.w_down]
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
+        act = ops.linear_act(xn, self.w_up, ctx.workspace.rows("ffn.act", ctx.num_tokens, self.intermediate, ctx.dtype), self.activation)
         ops.linear(act, self.w_down, residual, ops.LINEAR_ACC_F32)

@@ -33,15 +33,20 @@ def make_part(kind: str, name: str, **params):
 def _register_builtin() -> None:
     from .attention import PagedAttention
     from .block import PreNormBlock
-    from .feed_forward import SwiGLU
+    from .delta import GatedDeltaRule
+    from .feed_forward import DenseMLP, SwiGLU
+    from .hyper import HyperBlock
     from .norms import RMSNorm
     from .rotary import NoPositionEncoding, Rotary
     register_part("mixer", "attention", PagedAttention)
+    register_part("mixer", "gated_delta", GatedDeltaRule)
     register_part("feed_forward", "swiglu", SwiGLU)
+    register_part("feed_forward", "dense", DenseMLP)
     register_part("norm", "rmsnorm", RMSNorm)
     register_part("position", "rotary", Rotary)
     register_part("position", "none", NoPositionEncoding)
     register_part("block", "pre_norm", PreNormBlock)
+    register_part("block", "hyper", HyperBlock)
 
 
 _register_builtin()

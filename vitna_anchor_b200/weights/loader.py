@@ -28,9 +28,13 @@ from .safetensors_io import CheckpointError, SafetensorsFile
 @dataclass(frozen=True)
 class WeightSpec:
     name: str
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]      # None for a size that the checkpoint itself gives (the rows of a table, say)
     optional: bool = False      # may be absent (the model says what stands in for it)
     floating: bool = True       # floating-point tensors; False for integer tables
+    free_size: int = 0          # what random initialisation takes for a size of None
+
+    def fits(self, shape) -> bool:
+        return len(shape) == len(self.shape) and all(w is None or w == g for w, g in zip(self.shape, shape))
 
 
 class WeightMismatch(CheckpointError):
@@ -89,8 +93,8 @@ def load_weights(model_dir: str, manifest: Sequence[WeightSpec]) -> Dict[str, to
             if sh is None:
                 continue
             e = sh.entries[w.name]
-            if tuple(e.shape) != tuple(w.shape):
-                wrong.append(f"{w.name} is {list(e.shape)}, the model needs {list(w.shape)}")
+            if not w.fits(tuple(e.shape)):
+                wrong.append(f"{w.name} is {list(e.shape)}, the model needs {['any' if d is None else d for d in w.shape]}")
             elif w.floating != (e.dtype in ("F32", "BF16", "F16")):
                 wrong.append(f"{w.name} has dtype {e.dtype}")
         if missing or wrong:

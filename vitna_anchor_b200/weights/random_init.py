@@ -5,7 +5,8 @@ same bytes on every machine: a counter-based splitmix64 stream per tensor
 (seeded from the run's seed and a hash of the tensor's name, so the order in
 which tensors are made does not matter), two 53-bit uniforms per pair of
 normals, Box-Muller in float64, then rounding to the stored dtype.
-Matrices and embeddings are N(0, std); norm weights are 1 + N(0, norm_noise).
+Matrices and embeddings are N(0, std); norm weights are 1 + N(0, norm_noise); a tensor for which the
+architecture's is_norm answers "identity" is the identity matrix + N(0, std).
 The reference has no such mode (its tests use real weights; the nearest
 precedent is the synthetic two-layer model of engine/tests/unit_tests.c:2180-2335).
 """
@@ -58,9 +59,13 @@ def random_weights(manifest: Sequence[WeightSpec], seed: int, *, is_norm: Callab
     for w in manifest:
         if w.optional:
             continue
-        n = int(np.prod(w.shape))
-        z = normal(w.name, seed, n).reshape(w.shape)
-        if is_norm(w.name):
+        shape = tuple(w.free_size if d is None else d for d in w.shape)
+        n = int(np.prod(shape))
+        z = normal(w.name, seed, n).reshape(shape)
+        kind = is_norm(w.name)
+        if kind == "identity":          # a square mixing matrix: the identity plus noise
+            out[w.name] = torch.from_numpy((np.eye(shape[0]) + std * z).astype(np.float32)).to(norm_dtype)
+        elif kind:
             out[w.name] = torch.from_numpy((1.0 + norm_noise * z).astype(np.float32)).to(norm_dtype)
         else:
             out[w.name] = torch.from_numpy((std * z).astype(np.float32)).to(matrix_dtype)
