@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--model 135M|360M|1.7B] [--workload decode|mixed|prefill8k]
+                    [--model 135M|360M|1.7B] [--workload decode|mixed|prefill8k|lupanex]
 
 The default run is SmolLM2-135M's sizes with random weights (N(0, 0.02), norm weights 1, seed 0) in
 bfloat16, a batch of 8 requests each decoding from its own 2,048-token random prompt, cache context
@@ -18,6 +18,10 @@ bfloat16, a batch of 8 requests each decoding from its own 2,048-token random pr
 
 --workload mixed: 32 requests with prompts of 16..2,048 random tokens (seeded), prompts run in portions of at
 most 512 tokens beside the decoded tokens of the others, 128 new tokens each, through Engine.step.
+--workload lupanex: the Lupanex design (attention with a bias by distance beside the gated delta rule, hyper-connected residual
+streams, dense gelu feed-forward) at two sets of layer sizes, random weights, beside a Llama model of the same width, depth and
+number of weights: a 2,048-token prompt and batch-8 decoding from 2,048-token prompts for both, and where a prompt's time goes,
+kind of kernel by kind of kernel, against each kind's own roofline (LUPANEX_SIZES below).
 --workload prefill8k: one 8,192-token prompt, in one step and in portions of 2,048 through the scheduler.
 
 --impl reference builds nothing of this repository's engine: it runs the unmodified reference program
@@ -254,7 +258,7 @@ def prefill_run(model, sizes, clocks, tokens=PREFILL_TOKENS, portion=0, repeats=
     ms = sorted(times)[len(times) // 2]
     del runner
     torch.cuda.empty_cache()
-    return {"value": tokens * 1e3 / ms, "tokens": tokens, "ms": ms, "flops": prefill_flops(sizes, tokens),
+    return {"value": tokens * 1e3 / ms, "tokens": tokens, "ms": ms, "flops": prefill_flops(sizes, tokens) if sizes else 0.0,
             "host_issue_ms": sorted(host)[len(host) // 2]}
 
 
@@ -460,6 +464,127 @@ def reference_run(steps, warmup):
     }
 
 
+
+# ---------------------------------------------------------------------------------------------------------------
+# --workload lupanex
+# ---------------------------------------------------------------------------------------------------------------
+
+# Two sets of layer sizes: those of a 135M-class and of a 2B-class model, cut to a dozen layers so that a run stays short.  Three
+# of four layers are delta layers, the fourth is attention; the dense feed-forward is 1.5 times as wide as the Llama model's
+# gated one, which gives both the same number of weights.
+LUPANEX_SIZES = {
+    "w576": dict(width=576, ff=2304, heads=9, kv=3, dim=64, vdim=64, layers=12, llama=dict(heads=9, kv=3, head_dim=64, inter=1536)),
+    "w2048": dict(width=2048, ff=12288, heads=16, kv=4, dim=128, vdim=128, layers=8, llama=dict(heads=32, kv=8, head_dim=64, inter=8192)),
+}
+LUPANEX_VOCAB, LUPANEX_STREAMS = 49152, 2
+
+
+def lupanex_config(sz):
+    att = dict(heads=sz["heads"], kv_heads=sz["kv"], dim=sz["dim"], vdim=sz["vdim"], scale=sz["dim"] ** -0.5, bias_max=1024,
+               q_temp=dict(coef=0.1, every=256))
+    dl = dict(heads=sz["heads"], kv_heads=sz["kv"], dim=sz["dim"], vdim=sz["vdim"], conv=4)
+    mlp = dict(kind="dense", ff=sz["ff"])
+    layers = [dict(type="attention" if i % 4 == 3 else "delta", mixer=att if i % 4 == 3 else dl, mlp=mlp) for i in range(sz["layers"])]
+    return dict(architecture="Lupanex", vocab=LUPANEX_VOCAB, width=sz["width"], max_positions=CONTEXT, embedding=dict(scale=1.0),
+                norm=dict(eps=1e-6), streams=LUPANEX_STREAMS, layers=layers)
+
+
+def llama_like(sz):
+    l = sz["llama"]
+    return dict(num_hidden_layers=sz["layers"], hidden_size=sz["width"], intermediate_size=l["inter"], num_attention_heads=l["heads"],
+                num_key_value_heads=l["kv"], head_dim=l["head_dim"], vocab_size=LUPANEX_VOCAB, max_position_embeddings=CONTEXT,
+                rms_norm_eps=1e-6, rope_theta=100000.0, tie_word_embeddings=True)
+
+
+def lupanex_work(sz, T):
+    """Algorithmic work of one T-token prompt, by kind of kernel: (flops, bytes)."""
+    W, L, s = sz["width"], sz["layers"], LUPANEX_STREAMS
+    n_att = L // 4
+    n_delta = L - n_att
+    H, G, dk, dv = sz["heads"], sz["kv"], sz["dim"], sz["vdim"]
+    att_rows, delta_rows = (H + G) * dk + G * dv, 2 * G * dk + 2 * H * dv + 2 * H
+    products = 2.0 * T * W * (n_att * (att_rows + H * dv) + n_delta * (delta_rows + H * dv) + L * 2 * sz["ff"])
+    return {
+        "product": (products, 0.0),
+        "attention": (n_att * float(T) * (T + 1) * H * (dk + dv), 0.0),
+        "delta": (n_delta * 6.0 * T * H * dk * dv, n_delta * T * 4.0 * (2 * delta_rows + 2 * H * dv)),
+        "between": (0.0, (2 * L + 1) * T * W * (4.0 * (2 * s + 2) + 2)),
+    }
+
+
+def llama_work(c, T):
+    H, L, I = c["hidden_size"], c["num_hidden_layers"], c["intermediate_size"]
+    qd, kvd = c["num_attention_heads"] * c["head_dim"], c["num_key_value_heads"] * c["head_dim"]
+    return {"product": (2.0 * T * L * (H * (qd + 2 * kvd) + qd * H + 3 * H * I), 0.0),
+            "attention": (L * 4.0 * qd * T * (T + 1) / 2.0, 0.0),
+            "between": (0.0, 2 * L * T * H * 6.0)}
+
+
+def kind_of(launch):
+    if launch.startswith("linear"):
+        return "product"
+    if launch.startswith("attention"):
+        return "attention"
+    if launch.startswith("delta"):
+        return "delta"
+    if launch in ("hyper_step", "rmsnorm_rows"):
+        return "between"
+    return "other"
+
+
+def prompt_by_kind(model, work, pk, tokens=PREFILL_TOKENS):
+    """One prompt issued eagerly with an event behind every launch: milliseconds by kind of kernel, and each kind's share of its
+    roofline (the slower of its flops at the measured bf16 rate and its bytes at the measured copy rate, over the time it took)."""
+    import torch
+    from vitna_anchor_b200 import ops
+    from vitna_anchor_b200.engine.runner import ModelRunner, StepEntry
+    runner = ModelRunner(model, page_size=KV_BLOCK, num_pages=2 * tokens // KV_BLOCK, max_requests=2, max_batch_tokens=tokens,
+                         max_model_len=CONTEXT, cuda_graphs=False)
+    prompt = random_prompts(1, tokens, 2, model.vocab_size)[0]
+    times = None
+    for i in range(3):
+        runner.open(i)
+        times = ops.kernel_times(lambda: runner.step([StepEntry(i, prompt, [tokens - 1])]))
+        runner.check()
+        runner.close(i)
+    kinds, launches = {}, {}
+    for name, (n, ms) in times.items():
+        k = kind_of(name)
+        kinds[k] = kinds.get(k, 0.0) + ms
+        launches[name] = {"n": n, "ms": round(ms, 4)}
+    out = {}
+    for k, ms in kinds.items():
+        flops, nbytes = work.get(k, (0.0, 0.0))
+        ideal = max(flops / (pk["bf16_tflops"] * 1e12), nbytes / (pk["hbm_gbs"] * 1e9)) * 1e3
+        out[k] = {"ms": round(ms, 4), "roofline_ms": round(ideal, 4), "frac": round(ideal / ms, 4) if ms > 0 else None}
+    del runner
+    torch.cuda.empty_cache()
+    return {"kinds": out, "launches": launches}
+
+
+def lupanex_run(a, pk, clocks):
+    import torch
+    from vitna_anchor_b200.engine.loading import random_model_on_device
+    results = {}
+    for name, sz in LUPANEX_SIZES.items():
+        row = {}
+        for which, cfg, work in (("lupanex", lupanex_config(sz), lupanex_work(sz, PREFILL_TOKENS)),
+                                 ("llama", config_json(llama_like(sz)), llama_work(llama_like(sz), PREFILL_TOKENS))):
+            model = random_model_on_device(cfg, 0)
+            pf = prefill_run(model, None, clocks, repeats=3)
+            dec = decode_run(model, a.batch, min(a.steps, 32), a.warmup, clocks, with_e2e=False)
+            flops = sum(f for f, _ in work.values())
+            row[which] = {"weights_mb": round(model.step_weight_bytes() / 1e6, 1),
+                          "prefill_2048": {"tokens_per_s": round(pf["value"]), "ms": round(pf["ms"], 3),
+                                           "frac_bf16": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                          f"decode_b{a.batch}": {"tokens_per_s": round(dec["value"]), "ms_per_step": round(dec["ms_per_step"], 4),
+                                                 "frac_hbm": round(dec["gbs"] / pk["hbm_gbs"], 4), "launches_per_step": dec["launches"] // min(a.steps, 32)},
+                          "prompt_by_kind": prompt_by_kind(model, work, pk)}
+            del model
+            torch.cuda.empty_cache()
+        results[name] = row
+    return results
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -468,8 +593,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="135M", choices=sorted(MODELS), help="layer sizes: SmolLM2-135M (the default), 360M or 1.7B")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k"],
-                    help="decode (the default line), mixed (32 requests, 512-token portions beside decodes), prefill8k")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex"],
+                    help="decode (the default line), mixed (32 requests, 512-token portions beside decodes), prefill8k, lupanex "
+                         "(the Lupanex design beside a Llama model of equal size)")
     ap.add_argument("--no-points", action="store_true", help="skip the other batches, models and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="run the prefill measurement alone (for profiling)")
     ap.add_argument("--profile-region", default="", choices=["", "decode", "prefill"],
@@ -497,6 +623,14 @@ def main():
     clocks.start()
     if a.only_gemm:
         print(json.dumps({"gemm_m2048": gemm_run(pk)}))
+        return 0
+    if a.workload == "lupanex":
+        r = lupanex_run(a, pk, clocks)
+        clocks.stop()
+        print(json.dumps({"metric": "Lupanex beside Llama at equal width, depth and weights: tokens/s of a 2,048-token prompt and of "
+                          f"batch-{a.batch} decoding from 2,048-token prompts; a prompt's time by kind of kernel against its roofline",
+                          "impl": "ours", "dtype": "bf16", "data": "synthetic: random weights drawn on the device, uniform-random token ids",
+                          "peaks": pk, "sizes": r, "clocks": clocks.summary()}))
         return 0
     if a.workload == "mixed":
         model = random_model_on_device(config_json(SIZES), 0) if a.model != "135M" else model_folder()

@@ -21,6 +21,10 @@
 // 256; any number of heads and groups; any page size that is a multiple of that vector width is
 // NOT required: rows are [page][k|v][kv head][slot][hd], so every row starts 16-byte aligned
 // when hd does.
+//
+// The CUDA-core kernel of this file also takes values of another size than the keys (vd; a page is then
+// [nkv][page_size][hd] keys followed by [nkv][page_size][vd] values, and the scratch rows are vd wide) and a bias by
+// distance added to the scaled score: dist_bias [max_dist][nh] float32, row min(pos - key, max_dist - 1).
 #include "common.cuh"
 
 namespace vk {
@@ -41,7 +45,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     const T* __restrict__ q, const T* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ positions, const int32_t* __restrict__ tok_list,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters, int nh, int nkv,
-    int hd, int page_size, int max_blocks, int max_splits, float scale, int window) {
+    int hd, int page_size, int max_blocks, int max_splits, float scale, int window, int vd, const float* __restrict__ dist_bias,
+    int max_dist) {
     constexpr int V = Vec16<T>::N;
     extern __shared__ float smem[];
     const int g = nh / nkv;
@@ -66,17 +71,17 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
 
     float* qs = smem;                                  // [G_TILE][hd]
     float* ps = qs + DEC_G_TILE * hd;                  // [G_TILE][SPLIT]
-    float* red = ps + DEC_G_TILE * DEC_SPLIT;          // [groups][hd], groups * hd = 8 warps * 32 lanes * V
-    const int lds = hd + V;                            // a staged row and 16 bytes: 16-byte reads stay free of bank conflicts
+    float* red = ps + DEC_G_TILE * DEC_SPLIT;          // [groups][vd], groups * vd = 8 warps * 32 lanes * V
+    const int lds = hd + V, ldv = vd + V;              // a staged row and 16 bytes: 16-byte reads stay free of bank conflicts
     T* sk = reinterpret_cast<T*>(red + DEC_THREADS * V);   // [SPLIT][lds]   (ASYNC only)
-    T* sv = sk + DEC_SPLIT * lds;                      // [SPLIT][lds]
+    T* sv = sk + DEC_SPLIT * lds;                      // [SPLIT][ldv]
     __shared__ float wred[DEC_THREADS / 32][DEC_G_TILE];
     __shared__ float stat_m[DEC_G_TILE], stat_l[DEC_G_TILE];
     __shared__ int is_last;
 
     const int32_t* bt = block_tables + (size_t)token_seg[t] * max_blocks;
-    const size_t page_stride = (size_t)2 * nkv * page_size * hd;
-    const size_t v_off = (size_t)nkv * page_size * hd;
+    const size_t page_stride = (size_t)nkv * page_size * (hd + vd);
+    const size_t v_base = (size_t)nkv * page_size * hd;        // where a page's values begin
     const int key = k0 + tid;
     const bool valid = tid < nkeys && key >= lo;
     // the page of this thread's key: from the step's metadata, which no kernel writes
@@ -87,14 +92,15 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
 
     if (ASYNC) {
         // consecutive threads take consecutive 16-byte pieces: a warp's request covers whole lines of a page
-        const int ch = hd / V;
+        const int chk = hd / V, ch = chk + vd / V;
         for (int c = tid; c < DEC_SPLIT * ch; c += DEC_THREADS) {
             const int kl = c / ch, part = c - kl * ch;
             const int kk = k0 + kl;
             if (kl < nkeys && kk >= lo) {
-                const T* kr = cache + (size_t)bt[kk / page_size] * page_stride + ((size_t)kvh * page_size + kk % page_size) * hd + part * V;
-                dec_cp_async16(sk + kl * lds + part * V, kr);
-                dec_cp_async16(sv + kl * lds + part * V, kr + v_off);
+                const T* pg = cache + (size_t)bt[kk / page_size] * page_stride;
+                const size_t in_page = (size_t)kvh * page_size + kk % page_size;
+                if (part < chk) dec_cp_async16(sk + kl * lds + part * V, pg + in_page * hd + part * V);
+                else dec_cp_async16(sv + kl * ldv + (part - chk) * V, pg + v_base + in_page * vd + (part - chk) * V);
             }
         }
     }
@@ -124,6 +130,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     }
 #pragma unroll
     for (int h = 0; h < DEC_G_TILE; h++) s[h] = valid ? s[h] * scale : -INFINITY;
+    if (dist_bias && valid) {
+        const float* brow = dist_bias + (size_t)(pos - key < max_dist ? pos - key : max_dist - 1) * nh + h0;
+#pragma unroll
+        for (int h = 0; h < DEC_G_TILE; h++)
+            if (h < gt) s[h] += brow[h];
+    }
 
     // block maximum of each head
 #pragma unroll
@@ -154,7 +166,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
     }
 
     // ---- sum of p * v: a row of v is read by hd/V lanes, 16 bytes each --------------------------
-    const int lpr = hd / V;                        // lanes per row
+    const int lpr = vd / V;                        // lanes per row
     const int rpw = 32 / lpr;                      // rows per warp per pass (lanes beyond rpw*lpr idle)
     const int r = lane / lpr, c = (lane % lpr) * V;
     const bool lane_on = r < rpw;
@@ -175,8 +187,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
                 const int row = base + i * groups;
                 if (row < nkeys && row >= row_lo) {
                     const int kk = k0 + row;
-                    const T* vr = ASYNC ? sv + row * lds
-                                        : cache + (size_t)bt[kk / page_size] * page_stride + v_off + ((size_t)kvh * page_size + kk % page_size) * hd;
+                    const T* vr = ASYNC ? sv + row * ldv
+                                        : cache + (size_t)bt[kk / page_size] * page_stride + v_base + ((size_t)kvh * page_size + kk % page_size) * vd;
                     load16<T>(vr + c, vf[i]);
                 } else {
 #pragma unroll
@@ -226,14 +238,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
         __syncthreads();
         if (writer) {
 #pragma unroll
-            for (int e = 0; e < V; e++) red[my_part * hd + c + e] = acc[h][e];
+            for (int e = 0; e < V; e++) red[my_part * vd + c + e] = acc[h][e];
         }
         __syncthreads();
-        for (int d = tid; d < hd; d += DEC_THREADS) {
+        for (int d = tid; d < vd; d += DEC_THREADS) {
             float o = 0.0f;
-            for (int gi = 0; gi < parts; gi++) o += red[gi * hd + d];
-            if (single) out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * (1.0f / stat_l[h]));
-            else part_o[(((size_t)zi * nh + h0 + h) * max_splits + split) * hd + d] = o;
+            for (int gi = 0; gi < parts; gi++) o += red[gi * vd + d];
+            if (single) out[((size_t)t * nh + h0 + h) * vd + d] = from_f32<T>(o * (1.0f / stat_l[h]));
+            else part_o[(((size_t)zi * nh + h0 + h) * max_splits + split) * vd + d] = o;
         }
     }
     if (single) return;
@@ -277,21 +289,21 @@ __global__ void __launch_bounds__(DEC_THREADS, 2) attention_decode_kernel(
         stat_l[tid] = 1.0f / l;
     }
     __syncthreads();
-    for (int i = tid; i < gt * hd; i += DEC_THREADS) {
-        const int h = i / hd, d = i % hd;
-        const float* po = part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * hd + d;
+    for (int i = tid; i < gt * vd; i += DEC_THREADS) {
+        const int h = i / vd, d = i % vd;
+        const float* po = part_o + (((size_t)zi * nh + h0 + h) * max_splits + first_split) * vd + d;
         float o = 0.0f;
         int j = 0;
         for (; j + 4 <= n_active; j += 4) {
-            const float a0 = __ldcg(po + (size_t)j * hd), a1 = __ldcg(po + (size_t)(j + 1) * hd);
-            const float a2 = __ldcg(po + (size_t)(j + 2) * hd), a3 = __ldcg(po + (size_t)(j + 3) * hd);
+            const float a0 = __ldcg(po + (size_t)j * vd), a1 = __ldcg(po + (size_t)(j + 1) * vd);
+            const float a2 = __ldcg(po + (size_t)(j + 2) * vd), a3 = __ldcg(po + (size_t)(j + 3) * vd);
             o += a0 * wsp[h * DEC_SPLIT + j];
             o += a1 * wsp[h * DEC_SPLIT + j + 1];
             o += a2 * wsp[h * DEC_SPLIT + j + 2];
             o += a3 * wsp[h * DEC_SPLIT + j + 3];
         }
-        for (; j < n_active; j++) o += __ldcg(po + (size_t)j * hd) * wsp[h * DEC_SPLIT + j];
-        out[((size_t)t * nh + h0 + h) * hd + d] = from_f32<T>(o * stat_l[h]);
+        for (; j < n_active; j++) o += __ldcg(po + (size_t)j * vd) * wsp[h * DEC_SPLIT + j];
+        out[((size_t)t * nh + h0 + h) * vd + d] = from_f32<T>(o * stat_l[h]);
     }
 }
 
@@ -368,7 +380,58 @@ VK_API int vk_attention_decode(const void* q, const void* cache, const int32_t* 
         }                                                                                                                            \
         return launch_dependent(kern, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, (const T*)cache, block_tables, token_seg, \
                                 positions, tok_list, (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, \
-                                scale, window);                                                                                      \
+                                scale, window, hd, (const float*)nullptr, 0);                                                        \
+    }
+    if (dtype == 0) {
+        if (async) GO(float, true) else GO(float, false)
+    } else {
+        if (async) GO(__nv_bfloat16, true) else GO(__nv_bfloat16, false)
+    }
+#undef GO
+    return launch_status();
+}
+
+// The same for the unrotated form of the attention: values of size vd (the scratch is
+// vk_attention_decode_scratch_bytes(tokens, nh, nkv, max(hd, vd), max_context) bytes) and an optional bias by distance.
+// Always the CUDA-core kernel, in both dtypes.
+VK_API int vk_attention_decode_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* token_seg,
+                                      const int32_t* positions, const int32_t* tok_list, void* out, void* scratch, int scratch_tokens,
+                                      int n_tokens, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, int max_context,
+                                      int grid_context, float scale, int window, const float* dist_bias, int max_dist, int dtype,
+                                      cudaStream_t stream) {
+    if (n_tokens <= 0) return VK_OK;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || vd <= 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || max_context <= 0 ||
+        grid_context <= 0 || grid_context > max_context || (dist_bias && max_dist <= 0))
+        return VK_BAD_SHAPE;
+    const int vec = dtype == 0 ? 4 : 8;
+    if (hd % vec != 0 || vd % vec != 0) return VK_BAD_SHAPE;
+    if (hd > DEC_MAX_HD || vd > DEC_MAX_HD || vd / vec > 32 || n_tokens > scratch_tokens || n_tokens > 65535 || max_context > 128 * DEC_SPLIT)
+        return VK_TOO_LARGE;
+    if (((uintptr_t)cache % 16) || ((uintptr_t)scratch % 16) || ((uintptr_t)q % 4)) return VK_BAD_ALIGNMENT;
+    const int splits = (max_context + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int grid_splits = (grid_context + DEC_SPLIT - 1) / DEC_SPLIT;
+    const int g = nh / nkv, tiles = nkv * ((g + DEC_G_TILE - 1) / DEC_G_TILE);
+    const int wide = hd > vd ? hd : vd;
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    char* base = (char*)scratch;
+    float* part_o = (float*)base;
+    float* part_ml = (float*)(base + up((size_t)scratch_tokens * nh * splits * wide * 4));
+    int* counters = (int*)((char*)part_ml + up((size_t)scratch_tokens * nh * splits * 2 * 4));
+    const size_t smem_base = (size_t)(DEC_G_TILE * hd + DEC_G_TILE * DEC_SPLIT + DEC_THREADS * vec) * sizeof(float);
+    const size_t smem_async = smem_base + (size_t)DEC_SPLIT * (hd + vd + 2 * vec) * (dtype == 0 ? 4 : 2);
+    const bool async = smem_async <= 100 * 1024;        // two blocks a multiprocessor
+    const size_t smem = async ? smem_async : smem_base;
+    dim3 grid(grid_splits, tiles, n_tokens);
+#define GO(T, A)                                                                                                                     \
+    {                                                                                                                                \
+        auto kern = attention_decode_kernel<T, A>;                                                                                   \
+        if (smem > 48 * 1024) {                                                                                                      \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+            if (e != cudaSuccess) return (int)e;                                                                                     \
+        }                                                                                                                            \
+        return launch_dependent(kern, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, (const T*)cache, block_tables, token_seg, \
+                                positions, tok_list, (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks, splits, \
+                                scale, window, vd, dist_bias, max_dist);                                                             \
     }
     if (dtype == 0) {
         if (async) GO(float, true) else GO(float, false)
@@ -447,7 +510,7 @@ VK_API int vk_attention_decode_static(const void* q, const void* cache, const in
         }                                                                                                                     \
         kern<<<grid, DEC_THREADS, smem, stream>>>((const T*)q, (const T*)cache, block_tables, token_seg, positions, tok_list, \
                                                   (T*)out, part_o, part_ml, counters, nh, nkv, hd, page_size, max_blocks,     \
-                                                  splits, scale, window);                                                     \
+                                                  splits, scale, window, hd, (const float*)nullptr, 0);                       \
     }
     if (dtype == 0) {
         if (async) GO(float, true) else GO(float, false)

@@ -14,6 +14,11 @@
 // that P V matches the float32 probabilities of the decode kernel instead of differing from it by a
 // rounding of every p.  Head sizes: multiples of 16 up to 128 that are instantiated below.
 //
+// Values may have another size than the keys (VD; a page is then [nkv][page_size][HD] keys followed by
+// [nkv][page_size][VD] values), and a bias by distance may be added to the scaled score: dist_bias [max_dist][nh]
+// float32, row min(pos - key, max_dist - 1).  A group stages the 127 biases a (query tile, key tile) pair can meet, for
+// its head, in shared memory beside the key tile; the scores then go to base 2 with the bias before the maximum.
+//
 // tiles [n_tiles][4] int32: first token (flat index), rows (1..64), position of the first token, segment.
 #include "common.cuh"
 
@@ -51,20 +56,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
+template <int HD, int VD>
 __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
-    int window) {
+    int window, const float* __restrict__ dist_bias, int max_dist) {
     typedef __nv_bfloat16 T;
     constexpr int LD = HD + 8;                      // padded row: 16-byte shifts keep ldmatrix free of bank conflicts
+    constexpr int LDV = VD + 8;
     constexpr int KSTEPS = HD / 16;                 // k-steps of Q K^T
-    constexpr int DBLK = HD / 8;                    // 8-wide blocks of the output
+    constexpr int DBLK = VD / 8;                    // 8-wide blocks of the output
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sq = reinterpret_cast<T*>(smem_raw);         // [64][LD]
     const int grp = threadIdx.x / PF_GROUP;         // which half of the key tiles
-    T* sk = sq + PF_BM * LD + grp * 4 * PF_BN * LD; // this group's [2][64][LD]
-    T* sv = sk + 2 * PF_BN * LD;                    // this group's [2][64][LD]
+    T* sk = sq + PF_BM * LD + grp * 2 * PF_BN * (LD + LDV); // this group's [2][64][LD]
+    T* sv = sk + 2 * PF_BN * LD;                    // this group's [2][64][LDV]
+    float* sb = reinterpret_cast<float*>(sq + PF_BM * LD + 4 * PF_BN * (LD + LDV)) + grp * 2 * 128;    // this group's [2][128] biases
 
     const int tile = gridDim.x - 1 - blockIdx.x;    // later tiles of a prompt have more keys: start them first
     const int h = blockIdx.y;
@@ -73,16 +80,19 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const int tid = threadIdx.x % PF_GROUP, warp = tid >> 5, lane = tid & 31;      // within the group
     const int g = lane >> 2, qd = lane & 3;
     const int32_t* bt = block_tables + (size_t)seg * max_blocks;
-    const size_t page_stride = (size_t)2 * nkv * page_size * HD;
-    const size_t v_off = (size_t)nkv * page_size * HD;
+    const size_t page_stride = (size_t)nkv * page_size * (HD + VD);
+    const size_t v_base = (size_t)nkv * page_size * HD;       // where a page's values begin
 
-    const float scale_log2 = scale * 1.4426950408889634f;
+    // with a bias the scores are turned into base-2 exponents (scale, bias and log2 e) before the maximum is taken
+    const float score_log2 = scale * 1.4426950408889634f;
+    const float scale_log2 = dist_bias ? 1.0f : score_log2;
     const int last_pos = pos0 + rows - 1;
     const int lo_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;     // lowest key any row needs
     const int kt0 = lo_first / PF_BN, kt1 = last_pos / PF_BN;                               // key tiles kt0 .. kt1
 
     // ---- loads ------------------------------------------------------------------------------------
     constexpr int CHUNKS = HD / 8;                  // 16-byte chunks per row
+    constexpr int CHUNKS_V = VD / 8;
     auto load_q = [&]() {
         for (int i = threadIdx.x; i < PF_BM * CHUNKS; i += PF_THREADS) {
             const int r = i / CHUNKS, c = i % CHUNKS;
@@ -93,18 +103,23 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     };
     auto load_kv = [&](int kt, int buf) {
         T* dk = sk + buf * PF_BN * LD;
-        T* dv = sv + buf * PF_BN * LD;
-        for (int i = tid; i < PF_BN * CHUNKS; i += PF_GROUP) {
-            const int r = i / CHUNKS, c = i % CHUNKS;
+        T* dv = sv + buf * PF_BN * LDV;
+        for (int i = tid; i < PF_BN * (CHUNKS + CHUNKS_V); i += PF_GROUP) {
+            const int r = i / (CHUNKS + CHUNKS_V), c = i % (CHUNKS + CHUNKS_V);
             const int key = kt * PF_BN + r;
+            T* dst = c < CHUNKS ? dk + r * LD + c * 8 : dv + r * LDV + (c - CHUNKS) * 8;
             if (key <= last_pos && key >= lo_first) {
-                const T* src = cache + (size_t)bt[key / page_size] * page_stride + ((size_t)kvh * page_size + key % page_size) * HD + c * 8;
-                cp_async16(dk + r * LD + c * 8, src);
-                cp_async16(dv + r * LD + c * 8, src + v_off);
+                const T* pg = cache + (size_t)bt[key / page_size] * page_stride;
+                const size_t in_page = (size_t)kvh * page_size + key % page_size;
+                cp_async16(dst, c < CHUNKS ? pg + in_page * HD + c * 8 : pg + v_base + in_page * VD + (c - CHUNKS) * 8);
             } else {                                // never read as a key (masked), but keep the values finite
-                *reinterpret_cast<uint4*>(dk + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
-                *reinterpret_cast<uint4*>(dv + r * LD + c * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
+        }
+        if (dist_bias && tid < 127) {               // entry e: distance pos0 - kt * 64 - 63 + e  (query row r, key column c: e = r + 63 - c)
+            int d = pos0 - kt * PF_BN - 63 + tid;
+            d = d < 0 ? 0 : (d < max_dist ? d : max_dist - 1);
+            sb[buf * 128 + tid] = dist_bias[(size_t)d * nh + h] * 1.4426950408889634f;
         }
     };
 
@@ -146,7 +161,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
             }
         }
         const T* k_s = sk + buf * PF_BN * LD;
-        const T* v_s = sv + buf * PF_BN * LD;
+        const T* v_s = sv + buf * PF_BN * LDV;
 
         // a warp whose 16 rows all lie before this key tile, or whose windows all lie after it, has nothing to add
         const int warp_last = pos0 + warp * 16 + 15;
@@ -166,6 +181,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
                     ldsm_x4(b0, b1, b2, b3, p);
                     mma16816(s[nb2 * 2], qf[ks], b0, b1);
                     mma16816(s[nb2 * 2 + 1], qf[ks], b2, b3);
+                }
+            }
+            if (dist_bias) {
+                const float* b_s = sb + buf * 128;
+#pragma unroll
+                for (int nb = 0; nb < 8; nb++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int rr = warp * 16 + g + (e >= 2 ? 8 : 0), cc = nb * 8 + qd * 2 + (e & 1);
+                        s[nb][e] = fmaf(s[nb][e], score_log2, b_s[rr + 63 - cc]);
+                    }
                 }
             }
             // ---- scale, mask, running softmax (in base 2: exp(x) = exp2(x * log2 e), folded into the scale) ----------
@@ -238,7 +264,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
 #pragma unroll
                 for (int db2 = 0; db2 < DBLK / 2; db2++) {   // two blocks of 8 dimensions per ldmatrix.x4.trans
                     uint32_t b0, b1, b2, b3;
-                    const T* p = v_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + db2 * 16 + (lane >> 4) * 8;
+                    const T* p = v_s + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + db2 * 16 + (lane >> 4) * 8;
                     ldsm_x4_trans(b0, b1, b2, b3, p);
                     mma16816(o[db2 * 2], pf[kk], b0, b1);
                     mma16816(o[db2 * 2 + 1], pf[kk], b2, b3);
@@ -253,7 +279,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
 
     // ---- the two groups' running results meet: group 1 hands over, group 0 folds it in after its own -----------
     __syncthreads();            // every key tile is consumed: the tile buffers are free
-    float* hand = reinterpret_cast<float*>(sq + PF_BM * LD + 4 * PF_BN * LD);     // group 1's buffers, [128][DBLK*4 + 4]
+    float* hand = reinterpret_cast<float*>(sq + PF_BM * LD + 2 * PF_BN * (LD + LDV));     // group 1's buffers, [128][DBLK*4 + 4]
     constexpr int HW = DBLK * 4 + 4;
     if (grp == 1) {
         float* mine = hand + tid * HW;
@@ -286,25 +312,43 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     for (int i = 0; i < DBLK; i++) {
         const int d = i * 8 + qd * 2;
         if (row_a < rows)
-            *reinterpret_cast<uint32_t*>(out + ((size_t)(tok0 + row_a) * nh + h) * HD + d) = pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(tok0 + row_a) * nh + h) * VD + d) = pack_bf16(o[i][0] * inv_a, o[i][1] * inv_a);
         if (row_b < rows)
-            *reinterpret_cast<uint32_t*>(out + ((size_t)(tok0 + row_b) * nh + h) * HD + d) = pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(tok0 + row_b) * nh + h) * VD + d) = pack_bf16(o[i][2] * inv_b, o[i][3] * inv_b);
     }
 }
 
-template <int HD>
+template <int HD, int VD>
 static int launch_prefill(const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
-                          int nkv, int page_size, int max_blocks, float scale, int window, cudaStream_t stream) {
-    constexpr int LD = HD + 8;
-    const size_t smem = (size_t)(PF_BM + 8 * PF_BN) * LD * 2;
-    auto kern = attention_prefill_kernel<HD>;
+                          int nkv, int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist,
+                          cudaStream_t stream) {
+    constexpr int LD = HD + 8, LDV = VD + 8;
+    size_t smem = (size_t)(PF_BM * LD + 4 * PF_BN * (LD + LDV)) * 2 + 4 * 128 * sizeof(float);
+    const size_t hand = (size_t)(PF_BM * LD + 2 * PF_BN * (LD + LDV)) * 2 + (size_t)PF_GROUP * (VD / 8 * 4 + 4) * sizeof(float);
+    if (hand > smem) smem = hand;                   // where group 1 hands its results over
+    auto kern = attention_prefill_kernel<HD, VD>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
     dim3 grid(n_tiles, nh);
     return launch_plain(kern, grid, dim3(PF_THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, tiles,
-                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window);
+                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist);
+}
+
+template <int HD>
+static int launch_prefill_v(int vd, const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
+                            int nkv, int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist,
+                            cudaStream_t stream) {
+#define GO(VD) return launch_prefill<HD, VD>(q, cache, bt, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, stream)
+    switch (vd) {
+        case 32: GO(32);
+        case 64: GO(64);
+        case 96: GO(96);
+        case 128: GO(128);
+    }
+#undef GO
+    return VK_BAD_SHAPE;
 }
 
 }  // namespace vk
@@ -320,9 +364,29 @@ VK_API int vk_attention_prefill(const void* q, const void* cache, const int32_t*
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
     if (nh > 65535) return VK_TOO_LARGE;
     if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
-#define GO(HD) return launch_prefill<HD>(q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, stream)
+#define GO(HD) return launch_prefill<HD, HD>(q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, nullptr, 0, stream)
     switch (hd) {
         case 16: GO(16);
+        case 32: GO(32);
+        case 64: GO(64);
+        case 96: GO(96);
+        case 128: GO(128);
+    }
+#undef GO
+    return VK_BAD_SHAPE;
+}
+
+// The same for the unrotated form of the attention: values of size vd (out [all tokens, nh*vd]; a page holds its keys, then
+// its values) and an optional bias by distance.  Head sizes 32, 64, 96 and 128 for keys and for values, in any pairing.
+VK_API int vk_attention_prefill_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* tiles, void* out,
+                                       int n_tiles, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, float scale, int window,
+                                       const float* dist_bias, int max_dist, cudaStream_t stream) {
+    if (n_tiles <= 0) return VK_OK;
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || (dist_bias && max_dist <= 0)) return VK_BAD_SHAPE;
+    if (nh > 65535) return VK_TOO_LARGE;
+    if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
+#define GO(HD) return launch_prefill_v<HD>(vd, q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, stream)
+    switch (hd) {
         case 32: GO(32);
         case 64: GO(64);
         case 96: GO(96);

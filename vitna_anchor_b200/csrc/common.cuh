@@ -86,6 +86,15 @@ template <> __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfl
     }
 }
 
+// An activation chosen at run time, for epilogues: 0 none, 1 gelu in its erf form 0.5 z (1 + erf(z / sqrt 2)), 2 gelu in
+// its tanh form, 3 silu.  (The element-wise kernel numbers them from 0 without "none".)
+__device__ __forceinline__ float activate_rt(int kind, float z) {
+    if (kind == 1) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) return z / (1.0f + expf(-z));
+    return z;
+}
+
 inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  A kernel launched with launch_dependent() may start while the kernel before it

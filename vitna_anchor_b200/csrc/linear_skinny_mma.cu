@@ -46,6 +46,7 @@ struct MmaParams {
     const int32_t* slot;
     __nv_bfloat16* cache;
     int nh, nkv, hd, page_size;
+    int act;                     // ME_SAME: an activation on the float32 sums before they are rounded (activate_rt; 0 none)
 };
 
 __device__ __forceinline__ void mm_cp_async16(void* dst, const void* src) {
@@ -77,6 +78,7 @@ __device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, in
     typedef __nv_bfloat16 T;
     if (EPI == ME_SAME) {
         T* o = reinterpret_cast<T*>(p.out) + (size_t)m * p.N;
+        if (p.act) { a0 = activate_rt(p.act, a0); a1 = activate_rt(p.act, a1); }
         o[r0] = __float2bfloat16_rn(a0);
         if (has1) o[r1] = __float2bfloat16_rn(a1);
     } else if (EPI == ME_F32) {
@@ -871,12 +873,12 @@ VK_API int vk_set_skinny_stream(int mode) {
 
 // The bfloat16 few-rows product on tensor cores.  Arguments as vk_linear_skinny; in addition K must be a
 // multiple of 32, and with the fused norm x's rows must be 16-byte aligned (ldx a multiple of 4).
-VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
-                                int M, int N, int K, int ldx, int epi, const int32_t* positions, const float* cos_t,
-                                const float* sin_t, const int32_t* slot, void* cache, int nh, int nkv, int hd, int page_size,
-                                cudaStream_t stream) {
+static int linear_skinny_mma_impl(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
+                                  int M, int N, int K, int ldx, int epi, const int32_t* positions, const float* cos_t,
+                                  const float* sin_t, const int32_t* slot, void* cache, int nh, int nkv, int hd, int page_size, int act,
+                                  cudaStream_t stream) {
     if (M <= 0 || N <= 0) return VK_OK;
-    if (K <= 0 || ldx < K || epi < 0 || epi > 4 || K % 32 != 0) return VK_BAD_SHAPE;
+    if (K <= 0 || ldx < K || epi < 0 || epi > 4 || K % 32 != 0 || act < 0 || act > 3 || (act && epi != ME_SAME)) return VK_BAD_SHAPE;
     if (M > 64) return VK_TOO_LARGE;
     if (((uintptr_t)w % 16) || ((uintptr_t)x % 16)) return VK_BAD_ALIGNMENT;
     if (norm_w ? (ldx % 4 != 0 || ((uintptr_t)norm_w % 16)) : (ldx % 8 != 0)) return VK_BAD_ALIGNMENT;
@@ -887,6 +889,21 @@ VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float*
             return VK_BAD_SHAPE;
     }
     MmaParams p{x, rows, norm_w, eps, (const __nv_bfloat16*)w, out, M, N, K, ldx, 0, 0, 0, 0, 1, 0, positions, cos_t, sin_t, slot,
-                (__nv_bfloat16*)cache, nh, nkv, hd, page_size};
+                (__nv_bfloat16*)cache, nh, nkv, hd, page_size, act};
     return norm_w ? mma_dispatch<true>(epi, p, stream) : mma_dispatch<false>(epi, p, stream);
+}
+
+VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
+                                int M, int N, int K, int ldx, int epi, const int32_t* positions, const float* cos_t,
+                                const float* sin_t, const int32_t* slot, void* cache, int nh, int nkv, int hd, int page_size,
+                                cudaStream_t stream) {
+    return linear_skinny_mma_impl(x, rows, norm_w, eps, w, out, M, N, K, ldx, epi, positions, cos_t, sin_t, slot, cache, nh, nkv, hd,
+                                  page_size, 0, stream);
+}
+
+// out (bfloat16) = act(x' @ w.T) for at most 64 rows: the activation (activate_rt) on the float32 sums in the epilogue.
+VK_API int vk_linear_skinny_mma_act(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
+                                    int M, int N, int K, int ldx, int act, cudaStream_t stream) {
+    return linear_skinny_mma_impl(x, rows, norm_w, eps, w, out, M, N, K, ldx, ME_SAME, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0,
+                                  act, stream);
 }

@@ -47,6 +47,7 @@ struct TcExtra {
     const int32_t* slot;
     __nv_bfloat16* cache;
     int nh, nkv, hd, page_size;
+    int act;                     // TC_SAME: an activation on the float32 sums before they are rounded (activate_rt; 0 none)
 };
 
 template <int BN, int EPI>
@@ -298,6 +299,10 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                     // nothing of this thread's to store
                 } else if (EPI == TC_SAME) {
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+                    if (ex.act) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) r[j] = __float_as_uint(activate_rt(ex.act, __uint_as_float(r[j])));
+                    }
                     if (whole && (N % 8 == 0)) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
@@ -599,6 +604,10 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                         const bool whole = col + 32 <= N;
                         if (EPI == TC_SAME) {
                             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col;
+                            if (ex.act) {
+#pragma unroll
+                                for (int q = 0; q < 32; q++) r[q] = __float_as_uint(activate_rt(ex.act, __uint_as_float(r[q])));
+                            }
                             if (whole && (N % 8 == 0)) {
 #pragma unroll
                                 for (int q = 0; q < 32; q += 8) {
@@ -747,10 +756,12 @@ using namespace vk;
 
 // x [M, K] bfloat16 with row stride ldx, w [N, K] bfloat16, out [M, N]: mode 0 bfloat16, 1 float32, 2 float32 +=.
 // K and ldx multiples of 8, pointers 16-byte aligned.  error: a word the kernel sets (non-zero) if a bounded wait ran out.
-VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int mode, int* error,
-                             cudaStream_t stream) {
+static int linear_tcgen05_impl(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int mode, int act, int* error,
+                               cudaStream_t stream) {
     if (M <= 0 || N <= 0) return VK_OK;
-    if (K <= 0 || ldx < K || mode < 0 || mode > 2 || !error) return VK_BAD_SHAPE;
+    if (K <= 0 || ldx < K || mode < 0 || mode > 2 || !error || act < 0 || act > 3 || (act && mode != 0)) return VK_BAD_SHAPE;
+    TcExtra ex{};
+    ex.act = act;
     if (K % 8 != 0 || ldx % 8 != 0) return VK_BAD_SHAPE;
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
     const int bn = N >= 2048 ? 128 : 64;
@@ -758,13 +769,13 @@ VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int
     if (wide_takes(M, N, K)) {
         CUtensorMap wx, ww;
         if (!make_map(&wx, x, M, K, ldx, TC_BM) || !make_map(&ww, w, N, K, K, TW_BN)) return VK_BAD_SHAPE;
-        if (mode == 0) return launch_wide<TC_SAME>(wx, ww, out, M, N, K, error, stream);
+        if (mode == 0) return launch_wide<TC_SAME>(wx, ww, out, M, N, K, error, stream, ex);
         if (mode == 1) return launch_wide<TC_F32>(wx, ww, out, M, N, K, error, stream);
         return launch_wide<TC_ACC>(wx, ww, out, M, N, K, error, stream);
     }
     CUtensorMap mx, mw;
     if (!make_map(&mx, x, M, K, ldx, TC_BM) || !make_map(&mw, w, N, K, K, bn)) return VK_BAD_SHAPE;
-#define GO(BN, EPI) return launch_tc<BN, EPI>(mx, mw, out, M, N, K, error, stream)
+#define GO(BN, EPI) return launch_tc<BN, EPI>(mx, mw, out, M, N, K, error, stream, ex)
     if (bn == 128) {
         if (mode == 0) GO(128, TC_SAME);
         if (mode == 1) GO(128, TC_F32);
@@ -774,6 +785,17 @@ VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int
     if (mode == 1) GO(64, TC_F32);
     GO(64, TC_ACC);
 #undef GO
+}
+
+VK_API int vk_linear_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int mode, int* error,
+                             cudaStream_t stream) {
+    return linear_tcgen05_impl(x, w, out, M, N, K, ldx, mode, 0, error, stream);
+}
+
+// out (bfloat16) = act(x @ w.T): the activation (activate_rt: 1 gelu erf, 2 gelu tanh, 3 silu) on the float32 sums in the epilogue.
+VK_API int vk_linear_tcgen05_act(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int act, int* error,
+                                 cudaStream_t stream) {
+    return linear_tcgen05_impl(x, w, out, M, N, K, ldx, 0, act, error, stream);
 }
 
 // x [M, K] bfloat16 (row stride ldx), w [2*inter, K] bfloat16 with gate rows then up rows, out [M, inter] bfloat16 =

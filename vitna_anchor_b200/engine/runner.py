@@ -21,6 +21,7 @@ decode rows in one pass (engine/src/api.c:2216-2225).  Here they are one call.
 """
 from __future__ import annotations
 
+import gc
 import os
 from collections import OrderedDict
 from dataclasses import dataclass
@@ -286,8 +287,17 @@ class ModelRunner:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count()
-        with torch.cuda.graph(graph):
-            self.model.forward(ctx, rows, out=out)
+        # No garbage collection while the stream captures: a collection that frees another runner's graphs (a process
+        # that has had several engines) destroys them through calls that CUDA refuses during a capture, and the capture is lost.
+        gc_was_on = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, rows, out=out)
+        finally:
+            if gc_was_on:
+                gc.enable()
         kernels = ops.launch_count() - before
         ops.add_launches(-kernels)            # capture does not run the kernels
         return graph, kernels

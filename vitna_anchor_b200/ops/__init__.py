@@ -69,10 +69,17 @@ def add_launches(n: int) -> None:
     _launches += n
 
 
+_timed = None       # while kernel_times() runs: [(name of the launch, event recorded behind it)]
+
+
 def _check(status: int, what: str) -> None:
     global _launches
     if status == 0:
         _launches += 1
+        if _timed is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            _timed.append((what, ev))
         return
     fn = lib().vk_error_string
     fn.restype = ctypes.c_char_p
@@ -80,6 +87,28 @@ def _check(status: int, what: str) -> None:
     if status < 0:
         raise KernelError(f"{what}: refused, {text}")
     raise KernelError(f"{what}: CUDA error {status}: {text}")
+
+
+def kernel_times(fn) -> dict:
+    """Run fn() with an event behind every launch of this library and return {launch name: (count, milliseconds)}: the time
+    from the end of the launch before it to its own end.  Exact where the stream stays busy (a prompt's step, issued eagerly);
+    where launches are shorter than the host takes to issue them, the gaps are counted too.  For measurements only."""
+    global _timed
+    torch.cuda.synchronize()
+    _timed = []
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    try:
+        fn()
+    finally:
+        events, _timed = _timed, None
+    torch.cuda.synchronize()
+    out, before = {}, first
+    for name, ev in events:
+        n, ms = out.get(name, (0, 0.0))
+        out[name] = (n + 1, ms + before.elapsed_time(ev))
+        before = ev
+    return out
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -817,14 +846,110 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
     return out
 
 
+def attention_decode_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
+                            positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, scratch_tokens: int, nh: int, nkv: int, hd: int,
+                            vd: int, page_size: int, scale: float, max_context: int, grid_context: int, window: int = 0,
+                            dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The split-key attention of single decoded tokens in the unrotated form: values of size vd, an optional bias by distance.
+    scratch: attention_decode_scratch_bytes(scratch_tokens, nh, nkv, max(hd, vd), max_context) bytes, zero at first use."""
+    _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
+    _req(scratch, "scratch", torch.uint8, 1)
+    T = q.shape[0]
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+        raise KernelError("attention_decode_biased: shapes do not fit the head counts")
+    if dist_bias is not None:
+        _req(dist_bias, "dist_bias", torch.float32, 2)
+        if dist_bias.shape[1] != nh:
+            raise KernelError("attention_decode_biased: the bias table is not [distances, heads]")
+    n = T
+    if tok_list is not None:
+        _req(tok_list, "tok_list", torch.int32, 1)
+        n = tok_list.shape[0]
+    if scratch.numel() < attention_decode_scratch_bytes(scratch_tokens, nh, nkv, max(hd, vd), max_context):
+        raise KernelError("attention_decode_biased: the scratch is too small")
+    _check(lib().vk_attention_decode_biased(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out),
+                                            _p(scratch), scratch_tokens, n, nh, nkv, hd, vd, page_size, block_tables.shape[1], max_context,
+                                            grid_context, ctypes.c_float(scale), window, _p(dist_bias),
+                                            0 if dist_bias is None else dist_bias.shape[0], _dt(q), _stream()), "attention_decode_biased")
+    return out
+
+
+BIASED_PREFILL_HEAD_SIZES = (32, 64, 96, 128)
+
+
+def attention_prefill_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor,
+                             nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float, window: int = 0,
+                             dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of prompt portions in bfloat16 on the tensor cores, in the unrotated form.  tiles int32 [n, 4]: first
+    token, rows (1..64), position of the first token, segment."""
+    _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16)
+    _req(block_tables, "block_tables", torch.int32, 2); _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
+    if (q.shape[1] != nh * hd or out.shape != (q.shape[0], nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size
+            or tiles.shape[1] != 4):
+        raise KernelError("attention_prefill_biased: shapes do not fit the head counts")
+    if hd not in BIASED_PREFILL_HEAD_SIZES or vd not in BIASED_PREFILL_HEAD_SIZES:
+        raise KernelError(f"attention_prefill_biased: head sizes {hd}, {vd} are not among {BIASED_PREFILL_HEAD_SIZES}")
+    if dist_bias is not None:
+        _req(dist_bias, "dist_bias", torch.float32, 2)
+        if dist_bias.shape[1] != nh:
+            raise KernelError("attention_prefill_biased: the bias table is not [distances, heads]")
+    _check(lib().vk_attention_prefill_biased(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), tiles.shape[0], nh, nkv, hd, vd,
+                                             page_size, block_tables.shape[1], ctypes.c_float(scale), window, _p(dist_bias),
+                                             0 if dist_bias is None else dist_bias.shape[0], _stream()), "attention_prefill_biased")
+    return out
+
+
 def attention_biased(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int,
                      page_size: int, scale: float, window: int = 0, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of a mixed batch over the paged cache in the unrotated form (values of their own size, a bias by
-    distance); `meta` is the page group's GroupMeta."""
-    return attention_rows_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size, scale,
-                                 window, dist_bias)
+    distance); `meta` is the page group's GroupMeta.  Single decoded tokens take the split-key kernel, tokens of prompt
+    portions the tensor-core kernel (bfloat16, head sizes it is built for); whatever is left, and the whole exact 32-bit
+    routing, takes attention_rows_biased, which takes every size."""
+    vec = 4 if q.dtype == torch.float32 else 8
+    exact = q.dtype == torch.float32 and _float32_exact
+    dec_ok = (bool(ctx.num_dec) and not exact and hd % vec == 0 and vd % vec == 0 and max(hd, vd) <= 256 and vd // vec <= 32
+              and ctx.workspace.max_context <= 128 * 256)
+    pre_ok = (bool(ctx.num_pre) and q.dtype == torch.bfloat16 and hd in BIASED_PREFILL_HEAD_SIZES and vd in BIASED_PREFILL_HEAD_SIZES
+              and ctx.pre_tiles is not None and q.data_ptr() % 16 == 0 and pages.data_ptr() % 16 == 0)
+    rows = lambda toks: attention_rows_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size,
+                                              scale, window, dist_bias, toks)
+    if dec_ok:
+        ws = ctx.workspace
+        cap, layout = ws.max_segments, ws.max_context
+        nbytes = attention_decode_scratch_bytes(cap, nh, nkv, max(hd, vd), layout)
+        scratch = ws.flat(f"att.decb/{nh}/{nkv}/{hd}/{vd}/{layout}", nbytes, torch.uint8, zero=True)
+        attention_decode_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, scratch, cap, nh, nkv, hd, vd, page_size,
+                                scale, layout, min(layout, max(1, ctx.max_context)), window, dist_bias, ctx.dec_tokens)
+    if pre_ok:
+        attention_prefill_biased(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, vd, page_size, scale, window, dist_bias)
+    if not dec_ok and not pre_ok:
+        return rows(None)
+    if ctx.num_pre and not pre_ok:
+        rows(ctx.pre_tokens)
+    if ctx.num_dec and not dec_ok:
+        rows(ctx.dec_tokens)
+    return out
 
 
 def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
-    """out = act(x @ w.T) in x's dtype; kind one of ACTIVATIONS."""
+    """out = act(x @ w.T) in x's dtype; kind one of ACTIVATIONS.  In bfloat16 the activation is the epilogue of the few-rows
+    tensor-core product (up to 64 rows) or of the tcgen05 product, on the float32 sums; elsewhere it is a launch of its own."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"linear_act: {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K and tuple(out.shape) == (M, N) and out.dtype == x.dtype:
+        _req(w, "w", torch.bfloat16, 2); _req(out, "out", torch.bfloat16, 2)
+        act = ACTIVATIONS[kind] + 1
+        if (skinny_takes(x.dtype, M, K, N) and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+                and w.data_ptr() % 16 == 0):
+            ldx = x.stride(0) if M > 1 else max(K, x.stride(0))
+            _check(lib().vk_linear_skinny_mma_act(_p(x), _p(None), _p(None), ctypes.c_float(0.0), _p(w), _p(out), M, N, K, ldx, act,
+                                                  _stream()), "linear_skinny_mma_act")
+            return out
+        if M > SKINNY_MAX_ROWS and tcgen05_takes(x, w) and out.data_ptr() % 16 == 0:
+            _check(lib().vk_linear_tcgen05_act(_p(x), _p(w), _p(out), M, N, K, x.stride(0), act, _p(error_word()), _stream()),
+                   "linear_tcgen05_act")
+            return out
     return activation(linear(x, w, out, LINEAR_SAME), kind)
