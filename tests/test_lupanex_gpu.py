@@ -307,7 +307,7 @@ def test_the_delta_rule_kernels_against_the_recurrence_written_out():
     """Segments of unequal length on scattered slots, a second step that continues from the state of the first."""
     from vitna_anchor_b200 import ops
     rng = np.random.default_rng(5)
-    for (G, H, dk, dv, taps) in ((1, 2, 16, 8, 3), (2, 2, 64, 128, 4), (1, 3, 40, 24, 1), (2, 4, 128, 64, 2)):
+    for (G, H, dk, dv, taps) in ((1, 2, 16, 8, 3), (2, 2, 64, 128, 4), (1, 3, 40, 24, 1), (2, 4, 128, 64, 2), (1, 2, 10, 12, 2), (1, 1, 256, 32, 2)):
         C, N = 2 * G * dk + H * dv, 2 * G * dk + 2 * H * dv + 2 * H
         lens1, lens2, slots = [5, 1, 19], [1, 7, 2], [3, 0, 2]
         conv = rng.standard_normal((C, taps)) * 0.6
@@ -323,7 +323,7 @@ def test_the_delta_rule_kernels_against_the_recurrence_written_out():
             token_seg = torch.tensor(np.repeat(np.arange(len(lens)), lens), dtype=torch.int32, device="cuda")
             out = torch.empty(T, H * dv, device="cuda")
             ops.delta_rule(f(rows), f(conv), f(a_log), f(dt_bias), f(nw), 1e-5, token_seg, seg_starts,
-                           torch.tensor(slots, dtype=torch.int32, device="cuda"), state, torch.empty(T, C + 2 * H, device="cuda"),
+                           torch.tensor(slots, dtype=torch.int32, device="cuda"), state, torch.empty(T, ops.delta_prep_width(G, H, dk, dv), device="cuda"),
                            torch.empty(T, H * dv, device="cuda"), out, G, H, dk, dv, taps)
             o = out.cpu().numpy()
             at = 0

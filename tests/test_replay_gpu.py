@@ -70,7 +70,7 @@ def _replay(model_dir, mode, out_dir, max_tokens, kv_block, monkeypatch):
         monkeypatch.setenv("VITNA_FLOAT32_FAST", "1")
     else:
         monkeypatch.delenv("VITNA_FLOAT32_FAST", raising=False)
-    return Replay(model_dir, dtype, out_dir, max_tokens, kv_block=kv_block)
+    return Replay(model_dir, dtype, out_dir, max_tokens, kv_block=kv_block, max_requests=8)      # some schedules here hold five requests
 
 
 @pytest.mark.parametrize("mode", ["float32", "float32-fast", "bfloat16"])

@@ -27,11 +27,13 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(
     __shared__ float scratch[32];
     __shared__ float m_s[HC_MAX_STREAMS * HC_MAX_STREAMS], b_s[HC_MAX_STREAMS], a_s[HC_MAX_STREAMS];
     const int t = blockIdx.x, tid = threadIdx.x;
-    if (tid < streams * streams && mix) m_s[tid] = mix[tid];
+    if (tid < streams * streams && mix) m_s[tid] = mix[tid];          // weights: no kernel writes them
     if (tid < streams) {
         if (out_w) b_s[tid] = out_w[tid];
         a_s[tid] = in_w ? in_w[tid] : 1.0f;
     }
+    dependency_wait();                                                // the rows and y come from the kernels before this one
+    let_dependents_start();
     __syncthreads();
     float* row = xs + (size_t)t * streams * width;
     float ss = 0.0f;
@@ -123,13 +125,19 @@ VK_API int vk_hyper_step(float* xs, float* y, const float* mix, const float* out
     const size_t smem = (size_t)width * sizeof(float);
     if (dtype == 0) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        hyper_step_kernel<float><<<tokens, HC_THREADS, smem, stream>>>(xs, y, mix, out_w, in_w, norm_w, eps, (float*)xn, sum_out, streams, width);
+        if (tokens > 64)        // a prompt: an ordinary launch (waiting blocks would hold places the kernel before still needs)
+            return launch_plain(hyper_step_kernel<float>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w, eps,
+                                (float*)xn, sum_out, streams, width);
+        return launch_dependent(hyper_step_kernel<float>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w, eps,
+                                (float*)xn, sum_out, streams, width);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        hyper_step_kernel<__nv_bfloat16><<<tokens, HC_THREADS, smem, stream>>>(xs, y, mix, out_w, in_w, norm_w, eps, (__nv_bfloat16*)xn, sum_out,
-                                                                                streams, width);
+        if (tokens > 64)
+            return launch_plain(hyper_step_kernel<__nv_bfloat16>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w,
+                                eps, (__nv_bfloat16*)xn, sum_out, streams, width);
+        return launch_dependent(hyper_step_kernel<__nv_bfloat16>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w,
+                                eps, (__nv_bfloat16*)xn, sum_out, streams, width);
     }
-    return launch_status();
 }
 
 VK_API int vk_embed_scaled(const void* table, const int32_t* ids, const int32_t* positions, const float* pos_table, float scale, float* xs,

@@ -816,8 +816,13 @@ def attention_rows_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tabl
 
 def delta_state_floats(G: int, H: int, dk: int, dv: int, taps: int) -> int:
     """Floats of one request's state in one layer: the transposed matrix state of every head, then the last taps-1
-    inputs of the short convolution."""
-    return H * dv * dk + max(0, taps - 1) * (2 * G * dk + H * dv)
+    inputs of the short convolution, rounded up to a multiple of four."""
+    return (H * dv * dk + max(0, taps - 1) * (2 * G * dk + H * dv) + 3) // 4 * 4
+
+
+def delta_prep_width(G: int, H: int, dk: int, dv: int) -> int:
+    """Floats of a row of the delta rule's scratch between its kernels: q | k | v | log decay | beta, padded to a multiple of four."""
+    return (2 * G * dk + H * dv + 2 * H + 3) // 4 * 4
 
 
 def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float,
@@ -825,7 +830,7 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
                o: torch.Tensor, out: torch.Tensor, G: int, H: int, dk: int, dv: int, taps: int) -> torch.Tensor:
     """The gated delta rule on a batch of segments, from the projections to the input of the output projection.
     proj float32 [T, 2 G dk + 2 H dv + 2 H] = q | k | v | gate | b | a;  conv_w float32 [2 G dk + H dv, taps];  a_log, dt_bias [H];
-    norm_w [dv];  state float32 [slots, delta_state_floats];  prep [T, 2 G dk + H dv + 2 H] and o [T, H dv] float32 scratch;
+    norm_w [dv];  state float32 [slots, delta_state_floats];  prep [T, delta_prep_width] and o [T, H dv] float32 scratch;
     out [T, H dv] in the compute dtype.  Three launches: prepare, recurrence (which also writes the state), gate."""
     C = 2 * G * dk + H * dv
     _req(proj, "proj", torch.float32, 2); _req(conv_w, "conv_w", torch.float32, 2); _req(a_log, "a_log", torch.float32, 1)
@@ -834,13 +839,13 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
     _req(token_seg, "token_seg", torch.int32, 1); _req(seg_starts, "seg_starts", torch.int32, 1); _req(seg_slots, "seg_slots", torch.int32, 1)
     T, S = proj.shape[0], seg_slots.shape[0]
     if (proj.shape[1] != C + H * dv + 2 * H or conv_w.shape != (C, taps) or a_log.shape[0] != H or dt_bias.shape[0] != H
-            or norm_w.shape[0] != dv or prep.shape != (T, C + 2 * H) or o.shape != (T, H * dv) or out.shape != (T, H * dv)
+            or norm_w.shape[0] != dv or prep.shape != (T, delta_prep_width(G, H, dk, dv)) or o.shape != (T, H * dv) or out.shape != (T, H * dv)
             or state.shape[1] != delta_state_floats(G, H, dk, dv, taps) or token_seg.shape[0] != T or seg_starts.shape[0] != S + 1):
         raise KernelError("delta_rule: shapes do not fit the head counts")
     stride = ctypes.c_size_t(state.stride(0))
     _check(lib().vk_delta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
                                   _p(prep), T, G, H, dk, dv, taps, _stream()), "delta_prepare")
-    _check(lib().vk_delta_recurrence(_p(prep), _p(proj), _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, G, H, dk, dv, taps,
+    _check(lib().vk_delta_recurrence(_p(prep), _p(proj), _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, T, G, H, dk, dv, taps,
                                      _stream()), "delta_recurrence")
     _check(lib().vk_delta_gate(_p(o), _p(proj), _p(norm_w), ctypes.c_float(eps), _p(out), T, G, H, dk, dv, _dt(out), _stream()), "delta_gate")
     return out

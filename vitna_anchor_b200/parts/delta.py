@@ -56,7 +56,7 @@ class GatedDeltaRule(Mixer):
         T, ws = ctx.num_tokens, ctx.workspace
         proj = ops.linear(xn, self.w_in, ws.rows("delta.proj", T, self.w_in.shape[0], torch.float32), ops.LINEAR_F32)
         out = ops.delta_rule(proj, self.conv, self.a_log, self.dt_bias, self.norm_weight, self.eps, ctx.token_seg, ctx.seg_starts,
-                             ctx.seg_slots, cache.state, ws.rows("delta.prep", T, self.channels + 2 * self.H, torch.float32),
+                             ctx.seg_slots, cache.state, ws.rows("delta.prep", T, ops.delta_prep_width(self.G, self.H, self.dk, self.dv), torch.float32),
                              ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
                              self.G, self.H, self.dk, self.dv, self.taps)
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
