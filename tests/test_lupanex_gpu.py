@@ -303,13 +303,18 @@ def test_activation_alone_and_in_the_epilogues(kind):
         assert np.abs(out.float().cpu().numpy() - want).max() < 2e-2 * max(1.0, np.abs(want).max())
 
 
-def test_the_delta_rule_kernels_against_the_recurrence_written_out():
-    """Segments of unequal length on scattered slots, a second step that continues from the state of the first."""
+@pytest.mark.parametrize("chunked", [False, True])
+def test_the_delta_rule_kernels_against_the_recurrence_written_out(chunked):
+    """Segments of unequal length on scattered slots, a second step that continues from the state of the first; token by token and
+    in the chunked form (segments that end inside a chunk, exactly at its end, and single tokens beside them)."""
     from vitna_anchor_b200 import ops
     rng = np.random.default_rng(5)
-    for (G, H, dk, dv, taps) in ((1, 2, 16, 8, 3), (2, 2, 64, 128, 4), (1, 3, 40, 24, 1), (2, 4, 128, 64, 2), (1, 2, 10, 12, 2), (1, 1, 256, 32, 2)):
+    sizes = ((1, 2, 16, 8, 3), (2, 2, 64, 128, 4), (1, 3, 40, 24, 1), (2, 4, 128, 64, 2), (1, 2, 10, 12, 2), (1, 1, 256, 32, 2))
+    for (G, H, dk, dv, taps) in sizes:
+        if chunked and not ops.delta_chunked_takes(G, H, dk, dv, taps):
+            continue
         C, N = 2 * G * dk + H * dv, 2 * G * dk + 2 * H * dv + 2 * H
-        lens1, lens2, slots = [5, 1, 19], [1, 7, 2], [3, 0, 2]
+        lens1, lens2, slots = ([70, 1, 128], [1, 97, 64], [3, 0, 2]) if chunked else ([5, 1, 19], [1, 7, 2], [3, 0, 2])
         conv = rng.standard_normal((C, taps)) * 0.6
         a_log, dt_bias, nw = rng.standard_normal(H) - 1, rng.standard_normal(H), 1 + 0.1 * rng.standard_normal(dv)
         proj_all = [rng.standard_normal((l1 + l2, N)) for l1, l2 in zip(lens1, lens2)]
@@ -324,7 +329,8 @@ def test_the_delta_rule_kernels_against_the_recurrence_written_out():
             out = torch.empty(T, H * dv, device="cuda")
             ops.delta_rule(f(rows), f(conv), f(a_log), f(dt_bias), f(nw), 1e-5, token_seg, seg_starts,
                            torch.tensor(slots, dtype=torch.int32, device="cuda"), state, torch.empty(T, ops.delta_prep_width(G, H, dk, dv), device="cuda"),
-                           torch.empty(T, H * dv, device="cuda"), out, G, H, dk, dv, taps)
+                           torch.empty(T, H * dv, device="cuda"), out, G, H, dk, dv, taps,
+                           chunk_scratch=torch.empty(ops.delta_chunked_scratch_floats(T, len(lens), H, dk, dv), device="cuda") if chunked else None)
             o = out.cpu().numpy()
             at = 0
             for i, n in enumerate(lens):

@@ -14,7 +14,7 @@
 
 namespace vk {
 
-constexpr int HC_MAX_STREAMS = 8;
+constexpr int HC_MAX_STREAMS = 8;        // sixteen cost the kernel three times its time (registers)
 constexpr int HC_THREADS = 256;
 
 // One block per token.  smem: u [width].

@@ -825,13 +825,28 @@ def delta_prep_width(G: int, H: int, dk: int, dv: int) -> int:
     return (2 * G * dk + H * dv + 2 * H + 3) // 4 * 4
 
 
+def delta_chunked_takes(G: int, H: int, dk: int, dv: int, taps: int) -> bool:
+    """Whether the chunked form of the delta rule takes these sizes (key size a multiple of 4 up to 128, value size a multiple of 4
+    up to 256)."""
+    return bool(lib().vk_delta_chunked_takes(G, H, dk, dv, taps))
+
+
+def delta_chunked_scratch_floats(tokens: int, segments: int, H: int, dk: int, dv: int) -> int:
+    fn = lib().vk_delta_chunked_scratch_bytes
+    fn.restype = ctypes.c_size_t
+    return int(fn(tokens, segments, H, dk, dv)) // 4
+
+
 def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float,
                token_seg: torch.Tensor, seg_starts: torch.Tensor, seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor,
-               o: torch.Tensor, out: torch.Tensor, G: int, H: int, dk: int, dv: int, taps: int) -> torch.Tensor:
+               o: torch.Tensor, out: torch.Tensor, G: int, H: int, dk: int, dv: int, taps: int,
+               chunk_scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The gated delta rule on a batch of segments, from the projections to the input of the output projection.
     proj float32 [T, 2 G dk + 2 H dv + 2 H] = q | k | v | gate | b | a;  conv_w float32 [2 G dk + H dv, taps];  a_log, dt_bias [H];
     norm_w [dv];  state float32 [slots, delta_state_floats];  prep [T, delta_prep_width] and o [T, H dv] float32 scratch;
-    out [T, H dv] in the compute dtype.  Three launches: prepare, recurrence (which also writes the state), gate."""
+    out [T, H dv] in the compute dtype.  Three launches: prepare, recurrence (which also writes the state), gate.  With
+    chunk_scratch (float32, delta_chunked_scratch_floats(T, segments, ...)) the recurrence runs in its chunked form, two launches:
+    what does not need the state for all chunks side by side, then the chunks of every request in order."""
     C = 2 * G * dk + H * dv
     _req(proj, "proj", torch.float32, 2); _req(conv_w, "conv_w", torch.float32, 2); _req(a_log, "a_log", torch.float32, 1)
     _req(dt_bias, "dt_bias", torch.float32, 1); _req(norm_w, "norm_w", torch.float32, 1); _req(state, "state", torch.float32, 2)
@@ -845,8 +860,17 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
     stride = ctypes.c_size_t(state.stride(0))
     _check(lib().vk_delta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
                                   _p(prep), T, G, H, dk, dv, taps, _stream()), "delta_prepare")
-    _check(lib().vk_delta_recurrence(_p(prep), _p(proj), _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, T, G, H, dk, dv, taps,
-                                     _stream()), "delta_recurrence")
+    if chunk_scratch is not None:
+        _req(chunk_scratch, "chunk_scratch", torch.float32, 1)
+        if chunk_scratch.numel() < delta_chunked_scratch_floats(T, S, H, dk, dv):
+            raise KernelError("delta_rule: the scratch of the chunked form is too small")
+        _check(lib().vk_delta_chunked(_p(prep), prep.shape[1], _p(proj), _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o),
+                                      _p(chunk_scratch), S, T, G, H, dk, dv, taps, _stream()), "delta_chunked")
+        global _launches
+        _launches += 1                              # two kernels
+    else:
+        _check(lib().vk_delta_recurrence(_p(prep), _p(proj), _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, T, G, H, dk, dv, taps,
+                                         _stream()), "delta_recurrence")
     _check(lib().vk_delta_gate(_p(o), _p(proj), _p(norm_w), ctypes.c_float(eps), _p(out), T, G, H, dk, dv, _dt(out), _stream()), "delta_gate")
     return out
 

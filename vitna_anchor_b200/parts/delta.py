@@ -25,6 +25,8 @@ from .base import Mixer, StepContext
 
 
 class GatedDeltaRule(Mixer):
+    CHUNKED_FROM = 64       # steps of more tokens than this run the recurrence in chunks
+
     def __init__(self, hidden: int, num_heads: int, num_key_heads: int, key_dim: int, value_dim: int, taps: int, w_in: torch.Tensor,
                  conv: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_weight: torch.Tensor, wo: torch.Tensor, eps: float):
         """w_in: the projections stacked by rows, q | k | v | g | b | a ([2 G dk + 2 H dv + 2 H, hidden], compute dtype);
@@ -55,8 +57,14 @@ class GatedDeltaRule(Mixer):
             raise ValueError("a recurrent mixer has no cache that another run could read")
         T, ws = ctx.num_tokens, ctx.workspace
         proj = ops.linear(xn, self.w_in, ws.rows("delta.proj", T, self.w_in.shape[0], torch.float32), ops.LINEAR_F32)
+        # a prompt's step takes the chunked form (the exact 32-bit routing keeps one kernel for every step)
+        scratch = None
+        if (T > self.CHUNKED_FROM and not (ctx.dtype == torch.float32 and ops.float32_exact())
+                and ops.delta_chunked_takes(self.G, self.H, self.dk, self.dv, self.taps)):
+            scratch = ws.flat(f"delta.chunks/{self.H}/{self.dk}/{self.dv}",
+                              ops.delta_chunked_scratch_floats(ws.max_tokens, ws.max_segments, self.H, self.dk, self.dv), torch.float32)
         out = ops.delta_rule(proj, self.conv, self.a_log, self.dt_bias, self.norm_weight, self.eps, ctx.token_seg, ctx.seg_starts,
                              ctx.seg_slots, cache.state, ws.rows("delta.prep", T, ops.delta_prep_width(self.G, self.H, self.dk, self.dv), torch.float32),
                              ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
-                             self.G, self.H, self.dk, self.dv, self.taps)
+                             self.G, self.H, self.dk, self.dv, self.taps, chunk_scratch=scratch)
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
