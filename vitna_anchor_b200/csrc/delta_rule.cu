@@ -30,8 +30,9 @@ constexpr int DR_DEPENDENT_TOKENS = 64;    // launches of up to this many tokens
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
 
-// One block per token.  smem: act [C].
-__global__ void __launch_bounds__(256) delta_prepare_kernel(
+// One block per token.  smem: act [C].  A channel's inputs are all asked for before any is used: with few tokens in the step
+// the kernel is as long as its chain of trips to memory.
+__global__ void __launch_bounds__(1024) delta_prepare_kernel(
     const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
     const int32_t* __restrict__ token_seg, const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots,
     const float* __restrict__ state, size_t state_stride, size_t conv_off, float* __restrict__ prep, int P, int G, int H, int dk, int dv,
@@ -46,14 +47,19 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(
     const int slot = seg_slots[seg];
     const float* old = slot >= 0 ? state + (size_t)slot * state_stride + conv_off : nullptr;   // [taps-1][C]
     for (int c = tid; c < C; c += blockDim.x) {
-        float acc = 0.0f;
-        for (int j = taps - 1; j >= 0; j--) {               // oldest input first
-            const int src = i - j;
-            float x;
-            if (src >= 0) x = proj[(size_t)(t - j) * N + c];
-            else x = old ? old[(size_t)(taps - 1 + src) * C + c] : 0.0f;
-            acc = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+        float x[DR_MAX_TAPS], w[DR_MAX_TAPS];
+#pragma unroll
+        for (int j = 0; j < DR_MAX_TAPS; j++) {
+            if (j < taps) {
+                const int src = i - j;
+                x[j] = src >= 0 ? proj[(size_t)(t - j) * N + c] : (old ? old[(size_t)(taps - 1 + src) * C + c] : 0.0f);
+                w[j] = conv_w[(size_t)c * taps + (taps - 1 - j)];
+            }
         }
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = DR_MAX_TAPS - 1; j >= 0; j--)          // oldest input first
+            if (j < taps) acc = fmaf(w[j], x[j], acc);
         act[c] = silu_f(acc);
     }
     __syncthreads();
@@ -328,6 +334,124 @@ __global__ void __launch_bounds__(256) delta_gate_kernel(const float* __restrict
     for (int d = lane; d < dv; d += 32) out[(size_t)unit * dv + d] = from_f32<T>(((in[d] * inv) * norm_w[d]) * silu_f(gate[d]));
 }
 
+// Single decoded tokens: everything between the projections and the output projection in ONE kernel.  grid (segments, G): a
+// block has a key head's q and k and the H/G value heads that read them, so every channel of the convolution belongs to one
+// block, which reads its memory, uses it and moves it on.  The state's columns (H/G * dv of them) are taken in passes of
+// 256 / R columns, R lanes a column, KPT values a lane in pieces of four as in the kernel above.
+template <typename T, int KPT>
+__global__ void __launch_bounds__(256) delta_decode_kernel(
+    const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+    const float* __restrict__ norm_w, float eps, const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots,
+    float* __restrict__ state, size_t state_stride, size_t conv_off, T* __restrict__ out, int G, int H, int dk, int dv, int taps, int R) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float scal[2];
+    const int seg = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    dependency_wait();
+    let_dependents_start();
+    const int slot = seg_slots[seg];
+    if (slot < 0) return;                                    // a padding segment of a captured batch
+    const int t = seg_starts[seg];
+    const int HG = H / G, C = 2 * G * dk + H * dv, N = C + H * dv + 2 * H;
+    const int dkp = R * KPT, cols = HG * dv;
+    float* row = state + (size_t)slot * state_stride;
+    float* cs = row + conv_off;                              // [taps-1][C]
+    float* q_s = sm;                                         // [dkp]
+    float* k_s = q_s + dkp;                                  // [dkp]
+    float* v_s = k_s + dkp;                                  // [cols]
+    float* o_s = v_s + cols;                                 // [cols]
+    const float* in = proj + (size_t)t * N;
+
+    // the convolution with silu, and its memory moved on by the thread that read it
+    for (int idx = tid; idx < 2 * dkp + cols; idx += 256) {
+        int ch = -1;
+        if (idx < dkp) { if (idx < dk) ch = g * dk + idx; }
+        else if (idx < 2 * dkp) { if (idx - dkp < dk) ch = (G + g) * dk + (idx - dkp); }
+        else ch = 2 * G * dk + g * cols + (idx - 2 * dkp);
+        float val = 0.0f;
+        if (ch >= 0) {
+            float x[DR_MAX_TAPS], w[DR_MAX_TAPS];
+#pragma unroll
+            for (int j = 0; j < DR_MAX_TAPS; j++)
+                if (j < taps) {
+                    x[j] = j == 0 ? in[ch] : cs[(size_t)(taps - 1 - j) * C + ch];
+                    w[j] = conv_w[(size_t)ch * taps + (taps - 1 - j)];
+                }
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = DR_MAX_TAPS - 1; j >= 0; j--)
+                if (j < taps) acc = fmaf(w[j], x[j], acc);
+            val = silu_f(acc);
+#pragma unroll
+            for (int rr = 0; rr < DR_MAX_TAPS; rr++)          // row rr becomes the input of taps-2-rr tokens ago
+                if (rr < taps - 1) cs[(size_t)rr * C + ch] = x[taps - 2 - rr];
+        }
+        sm[idx] = val;                                       // q_s, k_s and v_s lie in this order
+    }
+    __syncthreads();
+    if (warp < 2) {                                          // unit length for q (and dk^-1/2) and k
+        const float* v = warp == 0 ? q_s : k_s;
+        float ss = 0.0f;
+        for (int d = lane; d < dk; d += 32) ss = fmaf(v[d], v[d], ss);
+        ss = warp_sum(ss);
+        float inv = 1.0f / sqrtf(ss + 1e-6f);
+        if (warp == 0) inv *= 1.0f / sqrtf((float)dk);
+        if (lane == 0) scal[warp] = inv;
+    }
+    __syncthreads();
+    for (int d = tid; d < dk; d += 256) { q_s[d] *= scal[0]; k_s[d] *= scal[1]; }
+    __syncthreads();
+
+    const int r = tid % R, per_pass = 256 / R;
+    for (int c0 = 0; c0 < cols; c0 += per_pass) {
+        const int ci = c0 + tid / R;
+        const bool live = ci < cols;
+        const int hh = live ? ci / dv : 0, col = live ? ci % dv : 0, h = g * HG + hh;
+        const float b = in[C + H * dv + h], a = in[C + H * dv + H + h];
+        const float dec = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+        const float beta = 1.0f / (1.0f + expf(-b));
+        float* srow = row + ((size_t)h * dv + col) * dk;
+        float s[KPT];
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < KPT / 4; i++) {
+            const int k0 = (i * R + r) * 4;
+            const float4 v = (live && k0 < dk) ? *reinterpret_cast<const float4*>(srow + k0) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4 kv = *reinterpret_cast<const float4*>(k_s + k0);
+            s[4 * i] = v.x; s[4 * i + 1] = v.y; s[4 * i + 2] = v.z; s[4 * i + 3] = v.w;
+            a0 = fmaf(v.x, kv.x, fmaf(v.z, kv.z, a0));
+            a1 = fmaf(v.y, kv.y, fmaf(v.w, kv.w, a1));
+        }
+        float dot = a0 + a1;
+        for (int w = R >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+        const float u = beta * (v_s[live ? ci : 0] - dec * dot);
+        a0 = a1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < KPT / 4; i++) {
+            const int k0 = (i * R + r) * 4;
+            const float4 kv = *reinterpret_cast<const float4*>(k_s + k0), qv = *reinterpret_cast<const float4*>(q_s + k0);
+            const float x0 = fmaf(kv.x, u, dec * s[4 * i]), x1 = fmaf(kv.y, u, dec * s[4 * i + 1]);
+            const float x2 = fmaf(kv.z, u, dec * s[4 * i + 2]), x3 = fmaf(kv.w, u, dec * s[4 * i + 3]);
+            a0 = fmaf(x0, qv.x, fmaf(x2, qv.z, a0));
+            a1 = fmaf(x1, qv.y, fmaf(x3, qv.w, a1));
+            if (live && k0 < dk) *reinterpret_cast<float4*>(srow + k0) = make_float4(x0, x1, x2, x3);
+        }
+        float acc = a0 + a1;
+        for (int w = R >> 1; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+        if (live && r == 0) o_s[ci] = acc;
+    }
+    __syncthreads();
+    for (int hh = warp; hh < HG; hh += 8) {                  // o / rms(o) * w * silu(gate), a warp a head
+        const int h = g * HG + hh;
+        const float* ov = o_s + hh * dv;
+        float ss = 0.0f;
+        for (int d = lane; d < dv; d += 32) ss = fmaf(ov[d], ov[d], ss);
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+        for (int d = lane; d < dv; d += 32)
+            out[((size_t)t * H + h) * dv + d] = from_f32<T>(((ov[d] * inv) * norm_w[d]) * silu_f(in[C + (size_t)h * dv + d]));
+    }
+}
+
 }  // namespace vk
 
 using namespace vk;
@@ -354,8 +478,10 @@ VK_API int vk_delta_prepare(const float* proj, const float* conv_w, const float*
     if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     // few tokens (decoding): the launch may begin under the end of the kernel before it; a prompt's launches stay ordinary, since
     // blocks that wait for a long kernel before them would hold the places its own later blocks need
+    const int wide = (int)((C + 31) / 32 * 32);
+    const int threads = tokens <= DR_DEPENDENT_TOKENS ? (wide < 1024 ? wide : 1024) : 256;     // few tokens: a channel a thread
     if (tokens <= DR_DEPENDENT_TOKENS)
-        return launch_dependent(delta_prepare_kernel, dim3(tokens), dim3(256), smem, stream, proj, conv_w, a_log, dt_bias, token_seg, seg_starts,
+        return launch_dependent(delta_prepare_kernel, dim3(tokens), dim3(threads), smem, stream, proj, conv_w, a_log, dt_bias, token_seg, seg_starts,
                                 seg_slots, state, state_stride, (size_t)H * dv * dk, prep, P, G, H, dk, dv, taps);
     return launch_plain(delta_prepare_kernel, dim3(tokens), dim3(256), smem, stream, proj, conv_w, a_log, dt_bias, token_seg, seg_starts,
                         seg_slots, state, state_stride, (size_t)H * dv * dk, prep, P, G, H, dk, dv, taps);
@@ -420,4 +546,39 @@ VK_API int vk_delta_gate(const float* o, const float* proj, const float* norm_w,
     }
     if (dtype == 0) return launch_plain(delta_gate_kernel<float>, dim3(grid), dim3(256), 0, stream, o, proj, norm_w, eps, (float*)out, tokens, G, H, dk, dv);
     return launch_plain(delta_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, o, proj, norm_w, eps, (__nv_bfloat16*)out, tokens, G, H, dk, dv);
+}
+
+// Whether the one-kernel form for single decoded tokens takes these sizes.
+VK_API int vk_delta_decode_takes(int G, int H, int dk, int dv, int taps) {
+    return G > 0 && H > 0 && H % G == 0 && dk % 4 == 0 && dk >= 4 && dk <= 32 * DR_KPT && dv > 0 && taps >= 1 && taps <= DR_MAX_TAPS &&
+           (size_t)(2 * 32 * DR_KPT + 2 * (H / G) * dv) * sizeof(float) <= 160 * 1024;
+}
+
+// Every segment is ONE token.  proj as above; out [tokens][H*dv] in dtype; the state is read and written.
+VK_API int vk_delta_decode(const float* proj, const float* conv_w, const float* a_log, const float* dt_bias, const float* norm_w, float eps,
+                           const int32_t* seg_starts, const int32_t* seg_slots, float* state, size_t state_stride, void* out, int segments, int G,
+                           int H, int dk, int dv, int taps, int dtype, cudaStream_t stream) {
+    if (segments <= 0) return VK_OK;
+    if (!vk_delta_decode_takes(G, H, dk, dv, taps)) return VK_BAD_SHAPE;
+    if (((uintptr_t)state % 16) || state_stride % 4 || G > 65535) return VK_BAD_ALIGNMENT;
+    const int cols = (H / G) * dv;
+    int R = 1;
+    while ((dk + R - 1) / R > DR_KPT) R *= 2;                // a lane holds at most DR_KPT values of a column
+    while (R < 32 && cols * R * 2 <= 256 && (dk + R - 1) / R > 4) R *= 2;      // few columns: more lanes a column
+    int kpt = 4;
+    while (kpt * R < dk) kpt *= 2;
+    const size_t smem = (size_t)(2 * R * kpt + 2 * cols) * sizeof(float);
+#define GO(TT, K)                                                                                                                       \
+    {                                                                                                                                   \
+        auto kern = delta_decode_kernel<TT, K>;                                                                                         \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+        return launch_dependent(kern, dim3(segments, G), dim3(256), smem, stream, proj, conv_w, a_log, dt_bias, norm_w, eps, seg_starts, \
+                                seg_slots, state, state_stride, (size_t)H * dv * dk, (TT*)out, G, H, dk, dv, taps, R);                  \
+    }
+    if (dtype == 0) {
+        if (kpt == 4) GO(float, 4) else if (kpt == 8) GO(float, 8) else if (kpt == 16) GO(float, 16) else GO(float, 32)
+    } else {
+        if (kpt == 4) GO(__nv_bfloat16, 4) else if (kpt == 8) GO(__nv_bfloat16, 8) else if (kpt == 16) GO(__nv_bfloat16, 16) else GO(__nv_bfloat16, 32)
+    }
+#undef GO
 }

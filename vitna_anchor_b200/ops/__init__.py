@@ -825,6 +825,11 @@ def delta_prep_width(G: int, H: int, dk: int, dv: int) -> int:
     return (2 * G * dk + H * dv + 2 * H + 3) // 4 * 4
 
 
+def delta_decode_takes(G: int, H: int, dk: int, dv: int, taps: int) -> bool:
+    """Whether the one-kernel delta rule for single decoded tokens takes these sizes (key size a multiple of 4)."""
+    return bool(lib().vk_delta_decode_takes(G, H, dk, dv, taps))
+
+
 def delta_chunked_takes(G: int, H: int, dk: int, dv: int, taps: int) -> bool:
     """Whether the chunked form of the delta rule takes these sizes (key size a multiple of 4 up to 128, value size a multiple of 4
     up to 256)."""
@@ -840,13 +845,14 @@ def delta_chunked_scratch_floats(tokens: int, segments: int, H: int, dk: int, dv
 def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, norm_w: torch.Tensor, eps: float,
                token_seg: torch.Tensor, seg_starts: torch.Tensor, seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor,
                o: torch.Tensor, out: torch.Tensor, G: int, H: int, dk: int, dv: int, taps: int,
-               chunk_scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+               chunk_scratch: Optional[torch.Tensor] = None, single_tokens: bool = False) -> torch.Tensor:
     """The gated delta rule on a batch of segments, from the projections to the input of the output projection.
     proj float32 [T, 2 G dk + 2 H dv + 2 H] = q | k | v | gate | b | a;  conv_w float32 [2 G dk + H dv, taps];  a_log, dt_bias [H];
     norm_w [dv];  state float32 [slots, delta_state_floats];  prep [T, delta_prep_width] and o [T, H dv] float32 scratch;
     out [T, H dv] in the compute dtype.  Three launches: prepare, recurrence (which also writes the state), gate.  With
     chunk_scratch (float32, delta_chunked_scratch_floats(T, segments, ...)) the recurrence runs in its chunked form, two launches:
-    what does not need the state for all chunks side by side, then the chunks of every request in order."""
+    what does not need the state for all chunks side by side, then the chunks of every request in order.  With single_tokens
+    (every segment is one token; sizes that delta_decode_takes) everything is ONE launch."""
     C = 2 * G * dk + H * dv
     _req(proj, "proj", torch.float32, 2); _req(conv_w, "conv_w", torch.float32, 2); _req(a_log, "a_log", torch.float32, 1)
     _req(dt_bias, "dt_bias", torch.float32, 1); _req(norm_w, "norm_w", torch.float32, 1); _req(state, "state", torch.float32, 2)
@@ -858,6 +864,10 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
             or state.shape[1] != delta_state_floats(G, H, dk, dv, taps) or token_seg.shape[0] != T or seg_starts.shape[0] != S + 1):
         raise KernelError("delta_rule: shapes do not fit the head counts")
     stride = ctypes.c_size_t(state.stride(0))
+    if single_tokens and T == S and delta_decode_takes(G, H, dk, dv, taps):
+        _check(lib().vk_delta_decode(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(norm_w), ctypes.c_float(eps), _p(seg_starts), _p(seg_slots),
+                                     _p(state), stride, _p(out), S, G, H, dk, dv, taps, _dt(out), _stream()), "delta_decode")
+        return out
     _check(lib().vk_delta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
                                   _p(prep), T, G, H, dk, dv, taps, _stream()), "delta_prepare")
     if chunk_scratch is not None:

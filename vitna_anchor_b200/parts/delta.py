@@ -66,5 +66,6 @@ class GatedDeltaRule(Mixer):
         out = ops.delta_rule(proj, self.conv, self.a_log, self.dt_bias, self.norm_weight, self.eps, ctx.token_seg, ctx.seg_starts,
                              ctx.seg_slots, cache.state, ws.rows("delta.prep", T, ops.delta_prep_width(self.G, self.H, self.dk, self.dv), torch.float32),
                              ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
-                             self.G, self.H, self.dk, self.dv, self.taps, chunk_scratch=scratch)
+                             self.G, self.H, self.dk, self.dv, self.taps, chunk_scratch=scratch,
+                             single_tokens=ctx.decode_only and not (ctx.dtype == torch.float32 and ops.float32_exact()))
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
