@@ -337,9 +337,10 @@ __global__ void __launch_bounds__(256) delta_gate_kernel(const float* __restrict
 // Single decoded tokens: everything between the projections and the output projection in ONE kernel.  grid (segments, G): a
 // block has a key head's q and k and the H/G value heads that read them, so every channel of the convolution belongs to one
 // block, which reads its memory, uses it and moves it on.  The state's columns (H/G * dv of them) are taken in passes of
-// 256 / R columns, R lanes a column, KPT values a lane in pieces of four as in the kernel above.
+// blockDim / R columns, R lanes a column, KPT <= 16 values a lane in pieces of four as in the kernel above; the block is as wide
+// as the columns need (up to 1,024 threads), since every pass is a trip to memory.
 template <typename T, int KPT>
-__global__ void __launch_bounds__(256) delta_decode_kernel(
+__global__ void __launch_bounds__(1024) delta_decode_kernel(
     const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
     const float* __restrict__ norm_w, float eps, const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots,
     float* __restrict__ state, size_t state_stride, size_t conv_off, T* __restrict__ out, int G, int H, int dk, int dv, int taps, int R) {
@@ -362,7 +363,7 @@ __global__ void __launch_bounds__(256) delta_decode_kernel(
     const float* in = proj + (size_t)t * N;
 
     // the convolution with silu, and its memory moved on by the thread that read it
-    for (int idx = tid; idx < 2 * dkp + cols; idx += 256) {
+    for (int idx = tid; idx < 2 * dkp + cols; idx += blockDim.x) {
         int ch = -1;
         if (idx < dkp) { if (idx < dk) ch = g * dk + idx; }
         else if (idx < 2 * dkp) { if (idx - dkp < dk) ch = (G + g) * dk + (idx - dkp); }
@@ -398,10 +399,10 @@ __global__ void __launch_bounds__(256) delta_decode_kernel(
         if (lane == 0) scal[warp] = inv;
     }
     __syncthreads();
-    for (int d = tid; d < dk; d += 256) { q_s[d] *= scal[0]; k_s[d] *= scal[1]; }
+    for (int d = tid; d < dk; d += blockDim.x) { q_s[d] *= scal[0]; k_s[d] *= scal[1]; }
     __syncthreads();
 
-    const int r = tid % R, per_pass = 256 / R;
+    const int r = tid % R, per_pass = blockDim.x / R;
     for (int c0 = 0; c0 < cols; c0 += per_pass) {
         const int ci = c0 + tid / R;
         const bool live = ci < cols;
@@ -440,7 +441,7 @@ __global__ void __launch_bounds__(256) delta_decode_kernel(
         if (live && r == 0) o_s[ci] = acc;
     }
     __syncthreads();
-    for (int hh = warp; hh < HG; hh += 8) {                  // o / rms(o) * w * silu(gate), a warp a head
+    for (int hh = warp; hh < HG; hh += (int)(blockDim.x >> 5)) {                  // o / rms(o) * w * silu(gate), a warp a head
         const int h = g * HG + hh;
         const float* ov = o_s + hh * dv;
         float ss = 0.0f;
@@ -550,8 +551,8 @@ VK_API int vk_delta_gate(const float* o, const float* proj, const float* norm_w,
 
 // Whether the one-kernel form for single decoded tokens takes these sizes.
 VK_API int vk_delta_decode_takes(int G, int H, int dk, int dv, int taps) {
-    return G > 0 && H > 0 && H % G == 0 && dk % 4 == 0 && dk >= 4 && dk <= 32 * DR_KPT && dv > 0 && taps >= 1 && taps <= DR_MAX_TAPS &&
-           (size_t)(2 * 32 * DR_KPT + 2 * (H / G) * dv) * sizeof(float) <= 160 * 1024;
+    return G > 0 && H > 0 && H % G == 0 && dk % 4 == 0 && dk >= 4 && dk <= 32 * 16 && dv > 0 && taps >= 1 && taps <= DR_MAX_TAPS &&
+           (size_t)(2 * 32 * 16 + 2 * (H / G) * dv) * sizeof(float) <= 160 * 1024;
 }
 
 // Every segment is ONE token.  proj as above; out [tokens][H*dv] in dtype; the state is read and written.
@@ -563,22 +564,24 @@ VK_API int vk_delta_decode(const float* proj, const float* conv_w, const float* 
     if (((uintptr_t)state % 16) || state_stride % 4 || G > 65535) return VK_BAD_ALIGNMENT;
     const int cols = (H / G) * dv;
     int R = 1;
-    while ((dk + R - 1) / R > DR_KPT) R *= 2;                // a lane holds at most DR_KPT values of a column
+    while ((dk + R - 1) / R > 16) R *= 2;                    // a lane holds at most sixteen values of a column
     while (R < 32 && cols * R * 2 <= 256 && (dk + R - 1) / R > 4) R *= 2;      // few columns: more lanes a column
     int kpt = 4;
     while (kpt * R < dk) kpt *= 2;
+    const int want = (cols * R + 31) / 32 * 32;
+    const int threads = want < 256 ? 256 : (want > 1024 ? 1024 : want);
     const size_t smem = (size_t)(2 * R * kpt + 2 * cols) * sizeof(float);
 #define GO(TT, K)                                                                                                                       \
     {                                                                                                                                   \
         auto kern = delta_decode_kernel<TT, K>;                                                                                         \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
-        return launch_dependent(kern, dim3(segments, G), dim3(256), smem, stream, proj, conv_w, a_log, dt_bias, norm_w, eps, seg_starts, \
+        return launch_dependent(kern, dim3(segments, G), dim3(threads), smem, stream, proj, conv_w, a_log, dt_bias, norm_w, eps, seg_starts, \
                                 seg_slots, state, state_stride, (size_t)H * dv * dk, (TT*)out, G, H, dk, dv, taps, R);                  \
     }
     if (dtype == 0) {
-        if (kpt == 4) GO(float, 4) else if (kpt == 8) GO(float, 8) else if (kpt == 16) GO(float, 16) else GO(float, 32)
+        if (kpt == 4) GO(float, 4) else if (kpt == 8) GO(float, 8) else GO(float, 16)
     } else {
-        if (kpt == 4) GO(__nv_bfloat16, 4) else if (kpt == 8) GO(__nv_bfloat16, 8) else if (kpt == 16) GO(__nv_bfloat16, 16) else GO(__nv_bfloat16, 32)
+        if (kpt == 4) GO(__nv_bfloat16, 4) else if (kpt == 8) GO(__nv_bfloat16, 8) else GO(__nv_bfloat16, 16)
     }
 #undef GO
 }

@@ -17,9 +17,10 @@ namespace vk {
 constexpr int HC_MAX_STREAMS = 8;        // sixteen cost the kernel three times its time (registers)
 constexpr int HC_THREADS = 256;
 
-// One block per token.  smem: u [width].
+// One block per token (256 threads; 1,024 for a step of few tokens, where the kernel is as long as its trips to memory and a
+// thread should have one column).  smem: u [width].
 template <typename T>
-__global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(
+__global__ void __launch_bounds__(1024) hyper_step_kernel(
     float* __restrict__ xs, float* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ out_w,
     const float* __restrict__ in_w, const float* __restrict__ norm_w, float eps, T* __restrict__ xn, float* __restrict__ sum_out,
     int streams, int width) {
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(
     __syncthreads();
     float* row = xs + (size_t)t * streams * width;
     float ss = 0.0f;
-    for (int c = tid; c < width; c += HC_THREADS) {
+    for (int c = tid; c < width; c += blockDim.x) {
         float x[HC_MAX_STREAMS];
 #pragma unroll
         for (int i = 0; i < HC_MAX_STREAMS; i++) x[i] = i < streams ? row[(size_t)i * width + c] : 0.0f;
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(
     if (!xn) return;
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    for (int c = tid; c < width; c += HC_THREADS) xn[(size_t)t * width + c] = from_f32<T>((u_s[c] * inv) * norm_w[c]);
+    for (int c = tid; c < width; c += blockDim.x) xn[(size_t)t * width + c] = from_f32<T>((u_s[c] * inv) * norm_w[c]);
 }
 
 // xs[t][j][:] = scale * table[ids[t]][:] + pos_table[positions[t]][:] for every copy j (pos_table may be null).
@@ -123,19 +124,20 @@ VK_API int vk_hyper_step(float* xs, float* y, const float* mix, const float* out
         return VK_BAD_SHAPE;
     if (streams > HC_MAX_STREAMS || (size_t)width * sizeof(float) > 200 * 1024) return VK_TOO_LARGE;
     const size_t smem = (size_t)width * sizeof(float);
+    const int threads = tokens > 64 ? HC_THREADS : (width >= 1024 ? 1024 : (width + 31) / 32 * 32 < HC_THREADS ? HC_THREADS : (width + 31) / 32 * 32);
     if (dtype == 0) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (tokens > 64)        // a prompt: an ordinary launch (waiting blocks would hold places the kernel before still needs)
-            return launch_plain(hyper_step_kernel<float>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w, eps,
+            return launch_plain(hyper_step_kernel<float>, dim3(tokens), dim3(threads), smem, stream, xs, y, mix, out_w, in_w, norm_w, eps,
                                 (float*)xn, sum_out, streams, width);
-        return launch_dependent(hyper_step_kernel<float>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w, eps,
+        return launch_dependent(hyper_step_kernel<float>, dim3(tokens), dim3(threads), smem, stream, xs, y, mix, out_w, in_w, norm_w, eps,
                                 (float*)xn, sum_out, streams, width);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (tokens > 64)
-            return launch_plain(hyper_step_kernel<__nv_bfloat16>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w,
+            return launch_plain(hyper_step_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, xs, y, mix, out_w, in_w, norm_w,
                                 eps, (__nv_bfloat16*)xn, sum_out, streams, width);
-        return launch_dependent(hyper_step_kernel<__nv_bfloat16>, dim3(tokens), dim3(HC_THREADS), smem, stream, xs, y, mix, out_w, in_w, norm_w,
+        return launch_dependent(hyper_step_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, xs, y, mix, out_w, in_w, norm_w,
                                 eps, (__nv_bfloat16*)xn, sum_out, streams, width);
     }
 }
