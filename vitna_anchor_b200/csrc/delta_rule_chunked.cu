@@ -189,12 +189,13 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __re
     float* row = state + (size_t)slot * state_stride;
 
     const int opnd = C * (3 * dk + C);      // floats of a chunk's W, Qg, KgT and P, which lie in this order
-    float* S_s = sm;                        // [dk][COLS]
-    float* U_s = S_s + dk * COLS;           // [C][COLS]
-    float* bufs = U_s + C * COLS;           // two buffers of `opnd` floats
+    const int lds = dk + 4, ldu = C + 4;    // the state's and the updates' slices are kept transposed: a column's values lie together,
+    float* S_s = sm;                        // [COLS][dk + 4]        so that every load below is 16 bytes
+    float* U_s = S_s + COLS * lds;          // [COLS][C + 4]
+    float* bufs = U_s + COLS * ldu;         // two buffers of `opnd` floats
     for (int e = tid; e < dk * COLS; e += T) {
-        const int d = e / COLS, cc = part * COLS + e % COLS;
-        S_s[e] = cc < dv ? row[((size_t)h * dv + cc) * dk + d] : 0.0f;
+        const int cc = e / dk, d = e - cc * dk, gc = part * COLS + cc;
+        S_s[cc * lds + d] = gc < dv ? row[((size_t)h * dv + gc) * dk + d] : 0.0f;
     }
     for (int e = tid; e < opnd / 4; e += T) dc_cp_async16(bufs + e * 4, scratch + ((size_t)base * H + h) * stride + e * 4);
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __re
     for (int c0 = 0, b = base; c0 < n; c0 += C, b++, turn ^= 1) {
         const float* in = scratch + ((size_t)b * H + h) * stride;
         const int cn = n - c0 < C ? n - c0 : C;
-        __syncthreads();                                     // the other buffer and U are free, the state slice is written
+        __syncthreads();                                     // the other buffer is free, the state slice is written
         if (c0 + C < n) {
             const float* nxt = in + (size_t)H * stride;
             for (int e = tid; e < opnd / 4; e += T) dc_cp_async16(bufs + (turn ^ 1) * opnd + e * 4, nxt + e * 4);
@@ -213,83 +214,72 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __re
         const float* K_s = Q_s + C * dk;        // [dk][C]
         const float* P_s = K_s + C * dk;        // [C][C]
         const float* U_g = in + (size_t)opnd;
-        for (int j = 0; j < C / RG; j++) {
-            const int t = r0 + RG * j;
-            U_s[t * COLS + c] = live ? U_g[(size_t)t * dv + col] : 0.0f;
-        }
+        float up[C / RG];                                    // U' of this thread's places
+#pragma unroll
+        for (int j = 0; j < C / RG; j++) up[j] = live ? U_g[(size_t)(r0 + RG * j) * dv + col] : 0.0f;
         const float gC = U_g[(size_t)C * dv];
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
-        // U = U' - W S
-        float acc[C / RG];
+        // W S and Qg S together: the state's values are loaded once for both
+        float ws[C / RG], qs[C / RG];
 #pragma unroll
-        for (int j = 0; j < C / RG; j++) acc[j] = 0.0f;
+        for (int j = 0; j < C / RG; j++) ws[j] = qs[j] = 0.0f;
+        const float* sc = S_s + c * lds;
         for (int d = 0; d < dk; d += 4) {
-            const float s0 = S_s[d * COLS + c], s1 = S_s[(d + 1) * COLS + c], s2 = S_s[(d + 2) * COLS + c], s3 = S_s[(d + 3) * COLS + c];
+            const float4 sv = *reinterpret_cast<const float4*>(sc + d);
 #pragma unroll
             for (int j = 0; j < C / RG; j++) {
                 const float4 w = *reinterpret_cast<const float4*>(W_s + (r0 + RG * j) * dk + d);
-                acc[j] = fmaf(w.x, s0, fmaf(w.y, s1, fmaf(w.z, s2, fmaf(w.w, s3, acc[j]))));
+                const float4 q = *reinterpret_cast<const float4*>(Q_s + (r0 + RG * j) * dk + d);
+                ws[j] = fmaf(w.x, sv.x, fmaf(w.y, sv.y, fmaf(w.z, sv.z, fmaf(w.w, sv.w, ws[j]))));
+                qs[j] = fmaf(q.x, sv.x, fmaf(q.y, sv.y, fmaf(q.z, sv.z, fmaf(q.w, sv.w, qs[j]))));
             }
         }
-        float u_new[C / RG];
+        float* uc = U_s + c * ldu;
 #pragma unroll
-        for (int j = 0; j < C / RG; j++) u_new[j] = U_s[(r0 + RG * j) * COLS + c] - acc[j];
-        __syncthreads();
-#pragma unroll
-        for (int j = 0; j < C / RG; j++) U_s[(r0 + RG * j) * COLS + c] = u_new[j];
+        for (int j = 0; j < C / RG; j++) uc[r0 + RG * j] = up[j] - ws[j];          // U = U' - W S
         __syncthreads();
         // O = Qg S + P U
-#pragma unroll
-        for (int j = 0; j < C / RG; j++) acc[j] = 0.0f;
-        for (int d = 0; d < dk; d += 4) {
-            const float s0 = S_s[d * COLS + c], s1 = S_s[(d + 1) * COLS + c], s2 = S_s[(d + 2) * COLS + c], s3 = S_s[(d + 3) * COLS + c];
-#pragma unroll
-            for (int j = 0; j < C / RG; j++) {
-                const float4 w = *reinterpret_cast<const float4*>(Q_s + (r0 + RG * j) * dk + d);
-                acc[j] = fmaf(w.x, s0, fmaf(w.y, s1, fmaf(w.z, s2, fmaf(w.w, s3, acc[j]))));
-            }
-        }
         for (int i = 0; i < C; i += 4) {
-            const float u0 = U_s[i * COLS + c], u1 = U_s[(i + 1) * COLS + c], u2 = U_s[(i + 2) * COLS + c], u3 = U_s[(i + 3) * COLS + c];
+            const float4 uv = *reinterpret_cast<const float4*>(uc + i);
 #pragma unroll
             for (int j = 0; j < C / RG; j++) {
                 const float4 w = *reinterpret_cast<const float4*>(P_s + (r0 + RG * j) * C + i);
-                acc[j] = fmaf(w.x, u0, fmaf(w.y, u1, fmaf(w.z, u2, fmaf(w.w, u3, acc[j]))));
+                qs[j] = fmaf(w.x, uv.x, fmaf(w.y, uv.y, fmaf(w.z, uv.z, fmaf(w.w, uv.w, qs[j]))));
             }
         }
 #pragma unroll
         for (int j = 0; j < C / RG; j++) {
             const int t = r0 + RG * j;
-            if (live && t < cn) o[((size_t)(start + c0 + t) * H + h) * dv + col] = acc[j];
+            if (live && t < cn) o[((size_t)(start + c0 + t) * H + h) * dv + col] = qs[j];
         }
         // S <- e^(L_C) S + KgT U: a thread has rows r0 + RG * j of its column; the new values wait in registers until every
         // thread has read the old state
         float s_new[DC_MAX_DK / RG];
 #pragma unroll
-        for (int j = 0; j < DC_MAX_DK / RG; j++) {
-            const int d = r0 + RG * j;
-            if (d < dk) {
-                float a0 = 0.0f, a1 = 0.0f;
-                for (int i = 0; i < C; i += 4) {
+        for (int j = 0; j < DC_MAX_DK / RG; j++) s_new[j] = 0.0f;
+        for (int i = 0; i < C; i += 4) {
+            const float4 uv = *reinterpret_cast<const float4*>(uc + i);
+#pragma unroll
+            for (int j = 0; j < DC_MAX_DK / RG; j++) {
+                const int d = r0 + RG * j;
+                if (d < dk) {
                     const float4 w = *reinterpret_cast<const float4*>(K_s + d * C + i);
-                    a0 = fmaf(w.x, U_s[i * COLS + c], fmaf(w.z, U_s[(i + 2) * COLS + c], a0));
-                    a1 = fmaf(w.y, U_s[(i + 1) * COLS + c], fmaf(w.w, U_s[(i + 3) * COLS + c], a1));
+                    s_new[j] = fmaf(w.x, uv.x, fmaf(w.y, uv.y, fmaf(w.z, uv.z, fmaf(w.w, uv.w, s_new[j]))));
                 }
-                s_new[j] = fmaf(gC, S_s[d * COLS + c], a0 + a1);
             }
         }
         __syncthreads();
 #pragma unroll
         for (int j = 0; j < DC_MAX_DK / RG; j++) {
             const int d = r0 + RG * j;
-            if (d < dk) S_s[d * COLS + c] = s_new[j];
+            if (d < dk) S_s[c * lds + d] = fmaf(gC, S_s[c * lds + d], s_new[j]);
         }
     }
     __syncthreads();
     for (int e = tid; e < dk * COLS; e += T) {
-        const int d = e / COLS, cc = part * COLS + e % COLS;
-        if (cc < dv) row[((size_t)h * dv + cc) * dk + d] = S_s[e];
+        const int cc = e / dk, d = e - cc * dk, gc = part * COLS + cc;
+        if (gc < dv) row[((size_t)h * dv + gc) * dk + d] = S_s[cc * lds + d];
     }
     // the convolution's memory: the last taps-1 inputs of the request, this step's tokens included
     if (taps > 1) {
@@ -340,7 +330,7 @@ VK_API int vk_delta_chunked(const float* prep, int prep_width, const float* proj
     const int chunks = tokens / C + segments;
     const size_t smem1 = (size_t)(2 * C * (dk + 1) + 2 * C * (C + 1) + C * (dv + dk)) * sizeof(float);
     constexpr int COLS = 16;
-    const size_t smem2 = (size_t)(dk * COLS + C * COLS + 2 * C * (3 * dk + C)) * sizeof(float);
+    const size_t smem2 = (size_t)(COLS * (dk + 4) + COLS * (C + 4) + 2 * C * (3 * dk + C)) * sizeof(float);
     const int parts = (dv + COLS - 1) / COLS;
     if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return VK_TOO_LARGE;
 #define GO(CC)                                                                                                                             \
