@@ -51,7 +51,7 @@ CFG_PLAIN = config(61, 48, [layer("delta", delta(2, 1, 16, 24, 2)),
 # four streams, a loop over the middle layer alone, three times; multi-query attention 3:1 with the query factor only
 CFG_STREAMS = config(83, 96, [layer("delta", delta(6, 2, 32, 16, 3), 64),
                               layer("attention", att(3, 1, 64, 32, 0.25, q_temp=(0.2, 5)), 128),
-                              layer("delta", delta(2, 2, 64, 64, 2))], streams=4, loop=(1, 2, 3), scale=3.0)
+                              layer("delta", delta(2, 2, 64, 64, 2))], streams=4, loop=(1, 2, 3), scale=2.5)
 # a single stream that still goes through hyper-connections
 CFG_ONE_STREAM = config(50, 32, [layer("attention", att(2, 1, 32, 32, 0.5, bias_max=10), 48), layer("delta", delta(1, 1, 32, 32, 2), 48)],
                         streams=1, loop=(1, 2, 1))

@@ -54,6 +54,13 @@ def test_what_the_engine_does_not_have_is_refused_by_name(change, word):
         LupanexConfig.from_dict(cj)
 
 
+def test_sizes_that_may_be_left_out():
+    cj = copy.deepcopy(LM.CONFIGS["plain"])
+    del cj["layers"][1]["mixer"]["kv_heads"], cj["layers"][1]["mixer"]["vdim"]
+    m = LupanexConfig.from_dict(cj).layers[1].mixer
+    assert (m.kv_heads, m.vdim) == (m.heads, m.dim)
+
+
 def test_distance_buckets():
     for rows, far in ((16, 100), (12, 40), (6, 9), (32, 128), (8, 512)):
         half = rows // 2

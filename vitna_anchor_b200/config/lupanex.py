@@ -91,10 +91,13 @@ class LayerSpec:
 
 
 def _heads(m: Mapping[str, Any], where: str):
-    heads, kv = _size(m, "heads", where), _size(m, "kv_heads", where)
+    """heads, kv_heads (the heads, if not given), dim, vdim (dim, if not given)."""
+    heads = _size(m, "heads", where)
+    kv = _size(m, "kv_heads", where) if m.get("kv_heads") is not None else heads
     if heads % kv:
         raise ConfigError(f"config.json: {where}heads do not divide into kv_heads groups")
-    return heads, kv, _size(m, "dim", where), _size(m, "vdim", where)
+    dim = _size(m, "dim", where)
+    return heads, kv, dim, _size(m, "vdim", where) if m.get("vdim") is not None else dim
 
 
 def _layer(i: int, entry: Mapping[str, Any]) -> LayerSpec:
