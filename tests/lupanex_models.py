@@ -1,7 +1,7 @@
 """Small Lupanex models for the tests: configurations of the tests' own, random weights of the tests' own making.
 
 None of the configurations is anybody's model.  Between them they vary what a single model would make equal: key
-heads per value head (1:1, 2:1, 3:1), sizes of keys against values, taps of the short convolution (1, 2, 4), residual
+heads per value head (1:1, 2:1, 3:1), sizes of keys against values, taps of the short convolution (1, 2, 3, 4), residual
 streams (none, 1, 2, 4), loops (none, once, three times, over one layer and over several), layers without a
 feed-forward, attention with and without the distance bias and the query factor, widths that the tensor-core kernels
 take and widths that they refuse.
