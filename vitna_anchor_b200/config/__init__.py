@@ -1,4 +1,5 @@
 from .errors import ConfigError  # noqa: F401
 from .llama import LlamaConfig, read_config_json  # noqa: F401
 from .lupanex import LupanexConfig  # noqa: F401
+from .siparax import SiparaxConfig  # noqa: F401
 from .registry import Architecture, architectures, register_architecture, resolve  # noqa: F401

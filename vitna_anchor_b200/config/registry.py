@@ -62,3 +62,7 @@ def _register_builtin() -> None:
     from .lupanex import ARCHITECTURE, LupanexConfig
     register_architecture(Architecture(ARCHITECTURE, LupanexConfig.from_dict, _lx.lupanex_manifest, _lx.build_lupanex,
                                        _lx.is_norm_weight), replace=True)
+    from ..models import siparax as _sx
+    from . import siparax as _sxc
+    register_architecture(Architecture(_sxc.ARCHITECTURE, _sxc.SiparaxConfig.from_dict, _sx.siparax_manifest, _sx.build_siparax,
+                                       _sx.is_norm_weight), replace=True)

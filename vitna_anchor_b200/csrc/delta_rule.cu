@@ -19,16 +19,9 @@
 //
 // Everything here is float32; only the result of 3 is rounded to the compute dtype for the output projection.
 // A request's per-layer state row is [H*dv*dk floats of S^T][(taps-1)*C floats of convolution inputs], C = 2 G dk + H dv.
-#include "common.cuh"
+#include "delta_common.cuh"
 
 namespace vk {
-
-constexpr int DR_MAX_TAPS = 16;
-constexpr int DR_KPT = 32;         // most values of a column one lane holds
-constexpr int DR_DEPENDENT_TOKENS = 64;    // launches of up to this many tokens are programmatic dependents
-
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
-__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
 
 // One block per token.  smem: act [C].  A channel's inputs are all asked for before any is used: with few tokens in the step
 // the kernel is as long as its chain of trips to memory.
@@ -80,13 +73,6 @@ __global__ void __launch_bounds__(1024) delta_prepare_kernel(
         out[C + h] = -expf(a_log[h]) * softplus_f(a + dt_bias[h]);       // the decay's logarithm; the recurrence takes exp of it
         out[C + H + h] = 1.0f / (1.0f + expf(-b));
     }
-}
-
-__device__ __forceinline__ void dr_cp_async4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void dr_cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
 // grid (segments, H, column parts); block = cols * R threads, thread = (column, lane of the column).  A lane holds KPT values

@@ -1,0 +1,150 @@
+// The steps of latent attention around its products and the attention itself.
+//
+// Queries, keys and values pass through narrow latents.  Of a token the cache keeps one row  [ c | kr ]:  the normed
+// key-value latent c (kv_rank values) and one rotated key part kr (rot_dim values) that all heads share.  With the keys'
+// and values' expansions folded into the neighbouring matrices, a head's query is  [ W_uk^T q_plain | rot(q_rot) ]
+// (kv_rank + rot_dim values), its score against a cached row their dot product, and its output the weighted sum of the
+// rows' c, which the folded output matrix takes on.  So the attention is one with a single key-value head whose key is the
+// row and whose value is the row's first kv_rank values.  A page of the cache layer is [page_size][kv_rank + rot_dim] keys
+// followed by [page_size][kv_rank] values (c once more, where the attention kernels expect values).
+//
+//  latent_prepare   one block a token, from the float32 row of the first product [ cq_raw | c_raw, kr_raw | ... ]:
+//                   cq = cq_raw / rms * w  to the compute dtype;  c = c_raw / rms * w  and  kr = rot(kr_raw, position)  into the
+//                   token's cache slot (a layer that reads another layer's cache has no such columns and writes nothing).
+//  latent_rotate_q  rotates the last rot_dim values of every head of the query product's result, in place.
+//  head_gate        multiplies head h of a token's rows by sigmoid of a float32 column of the first product, in place.
+//
+// Rotation: pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = (float)p * f_i, cos and sin times
+// `mag`; the pairs are (2i, 2i+1) (interleaved) or (i, i + dims/2) of the first `dims` values; f [dims/2] comes from the host
+// with any rescaling of the frequencies already in it.  Angles, cos and sin are float32 (accurate cosf and sinf).
+#include "common.cuh"
+
+namespace vk {
+
+__device__ __forceinline__ void rot_pair_index(int i, int dims, int interleaved, int& a, int& b) {
+    if (interleaved) { a = 2 * i; b = 2 * i + 1; }
+    else { a = i; b = i + dims / 2; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) latent_prepare_kernel(
+    const float* __restrict__ proj, int N, int q_rank, const float* __restrict__ qn_w, T* __restrict__ cq, int kv_off, int kv_rank,
+    int rot_dim, const float* __restrict__ kvn_w, float eps, const int32_t* __restrict__ positions, const float* __restrict__ freq,
+    float mag, int dims, int interleaved, const int32_t* __restrict__ slot, T* __restrict__ cache, int page_size) {
+    __shared__ float scratch[32];
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const float* in = proj + (size_t)t * N;
+    {
+        float ss = 0.0f;
+        for (int i = tid; i < q_rank; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)q_rank + eps);
+        for (int i = tid; i < q_rank; i += blockDim.x) cq[(size_t)t * q_rank + i] = from_f32<T>((in[i] * inv) * qn_w[i]);
+    }
+    if (kv_off < 0 || !cache || !slot) return;
+    const int s = slot[t];
+    if (s < 0) return;                                       // a padding token of a captured batch
+    const float* kv = in + kv_off;
+    float ss = 0.0f;
+    for (int i = tid; i < kv_rank; i += blockDim.x) ss = fmaf(kv[i], kv[i], ss);
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)kv_rank + eps);
+    const int hd = kv_rank + rot_dim;
+    const size_t page_stride = (size_t)page_size * (hd + kv_rank);
+    T* page = cache + (size_t)(s / page_size) * page_stride;
+    const int off = s % page_size;
+    T* krow = page + (size_t)off * hd;
+    T* vrow = page + (size_t)page_size * hd + (size_t)off * kv_rank;
+    for (int i = tid; i < kv_rank; i += blockDim.x) {
+        const T c = from_f32<T>((kv[i] * inv) * kvn_w[i]);
+        krow[i] = c;
+        vrow[i] = c;
+    }
+    const float* kr = kv + kv_rank;
+    const float pos = (float)positions[t];
+    for (int i = tid; i < dims / 2; i += blockDim.x) {
+        int a, b;
+        rot_pair_index(i, dims, interleaved, a, b);
+        const float ang = pos * freq[i];
+        const float c = cosf(ang) * mag, sn = sinf(ang) * mag;
+        const float u = kr[a], v = kr[b];
+        krow[kv_rank + a] = from_f32<T>(u * c - v * sn);
+        krow[kv_rank + b] = from_f32<T>(v * c + u * sn);
+    }
+    for (int i = dims + tid; i < rot_dim; i += blockDim.x) krow[kv_rank + i] = from_f32<T>(kr[i]);
+}
+
+// q [tokens][H][lat + rot_dim] in place; a thread a pair.
+template <typename T>
+__global__ void __launch_bounds__(256) latent_rotate_q_kernel(T* __restrict__ q, const int32_t* __restrict__ positions,
+                                                              const float* __restrict__ freq, float mag, int H, int lat, int rot_dim, int dims,
+                                                              int interleaved) {
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x, half = dims / 2;
+    const float pos = (float)positions[t];
+    T* row = q + (size_t)t * H * (lat + rot_dim);
+    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        int a, b;
+        rot_pair_index(i, dims, interleaved, a, b);
+        T* p = row + (size_t)h * (lat + rot_dim) + lat;
+        const float ang = pos * freq[i];
+        const float c = cosf(ang) * mag, sn = sinf(ang) * mag;
+        const float u = to_f32<T>(p[a]), v = to_f32<T>(p[b]);
+        p[a] = from_f32<T>(u * c - v * sn);
+        p[b] = from_f32<T>(v * c + u * sn);
+    }
+}
+
+// x [tokens][H][d] in place, times sigmoid(gates[t * N + off + h])
+template <typename T>
+__global__ void __launch_bounds__(256) head_gate_kernel(T* __restrict__ x, const float* __restrict__ gates, int N, int off, int H, int d) {
+    dependency_wait();
+    let_dependents_start();
+    const int t = blockIdx.x;
+    T* row = x + (size_t)t * H * d;
+    for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+        const float g = 1.0f / (1.0f + expf(-gates[(size_t)t * N + off + i / d]));
+        row[i] = from_f32<T>(to_f32<T>(row[i]) * g);
+    }
+}
+
+}  // namespace vk
+
+using namespace vk;
+
+// proj float32 [tokens][N]: columns 0..q_rank-1 the query latent, kv_off.. the key-value latent and the shared key part
+// (kv_off < 0: none).  cq [tokens][q_rank] and cache in dtype.  slot [tokens] (-1: no write).
+VK_API int vk_latent_prepare(const float* proj, int N, int q_rank, const float* qn_w, void* cq, int kv_off, int kv_rank, int rot_dim,
+                             const float* kvn_w, float eps, const int32_t* positions, const float* freq, float mag, int dims, int interleaved,
+                             const int32_t* slot, void* cache, int page_size, int tokens, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (q_rank <= 0 || N < q_rank || dims < 0 || dims % 2 || dims > rot_dim) return VK_BAD_SHAPE;
+    if (kv_off >= 0 && (kv_rank <= 0 || rot_dim < 0 || kv_off + kv_rank + rot_dim > N || page_size <= 0)) return VK_BAD_SHAPE;
+    if (dtype == 0)
+        return launch_dependent(latent_prepare_kernel<float>, dim3(tokens), dim3(256), 0, stream, proj, N, q_rank, qn_w, (float*)cq, kv_off, kv_rank,
+                                rot_dim, kvn_w, eps, positions, freq, mag, dims, interleaved, slot, (float*)cache, page_size);
+    return launch_dependent(latent_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, proj, N, q_rank, qn_w, (__nv_bfloat16*)cq,
+                            kv_off, kv_rank, rot_dim, kvn_w, eps, positions, freq, mag, dims, interleaved, slot, (__nv_bfloat16*)cache, page_size);
+}
+
+VK_API int vk_latent_rotate_q(void* q, const int32_t* positions, const float* freq, float mag, int tokens, int H, int lat, int rot_dim, int dims,
+                              int interleaved, int dtype, cudaStream_t stream) {
+    if (tokens <= 0 || dims == 0) return VK_OK;
+    if (H <= 0 || lat < 0 || dims < 0 || dims % 2 || dims > rot_dim) return VK_BAD_SHAPE;
+    if (dtype == 0)
+        return launch_dependent(latent_rotate_q_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)q, positions, freq, mag, H, lat, rot_dim, dims,
+                                interleaved);
+    return launch_dependent(latent_rotate_q_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)q, positions, freq, mag, H, lat,
+                            rot_dim, dims, interleaved);
+}
+
+VK_API int vk_head_gate(void* x, const float* gates, int N, int off, int tokens, int H, int d, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VK_OK;
+    if (H <= 0 || d <= 0 || off < 0 || off + H > N) return VK_BAD_SHAPE;
+    if (dtype == 0) return launch_dependent(head_gate_kernel<float>, dim3(tokens), dim3(256), 0, stream, (float*)x, gates, N, off, H, d);
+    return launch_dependent(head_gate_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (__nv_bfloat16*)x, gates, N, off, H, d);
+}

@@ -992,3 +992,139 @@ def linear_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str) -
                    "linear_tcgen05_act")
             return out
     return activation(linear(x, w, out, LINEAR_SAME), kind)
+
+
+# ---------------------------------------------------------------------------
+# Layer norm, the logits' soft cap, gated feed-forwards with any activation
+# ---------------------------------------------------------------------------
+
+def layernorm_rows(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out: torch.Tensor,
+                   rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r, :] = (x[rows[r], :] - mean) / sqrt(var + eps) * w + b; x float32 [T, n], out [R, n] float32 or bfloat16.
+    A float32 out may be x itself (rows not given)."""
+    _req(x, "x", torch.float32, 2); _req(w, "w", torch.float32, 1); _req(b, "b", torch.float32, 1); _req(out, "out", dims=2)
+    n = x.shape[1]
+    if w.shape[0] != n or b.shape[0] != n or out.shape[1] != n:
+        raise KernelError("layernorm_rows: widths differ")
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+        if rows.shape[0] != out.shape[0]:
+            raise KernelError("layernorm_rows: rows and out differ in length")
+    elif out.shape[0] != x.shape[0]:
+        raise KernelError("layernorm_rows: out and x differ in rows")
+    _check(lib().vk_layernorm_rows(_p(x), _p(w), _p(b), _p(rows), _p(out), out.shape[0], n, ctypes.c_float(eps), _dt(out), _stream()),
+           "layernorm_rows")
+    return out
+
+
+def softcap(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """z <- cap * tanh(z / cap), float32, in place."""
+    _req(z, "z", torch.float32)
+    _check(lib().vk_softcap(_p(z), ctypes.c_size_t(z.numel()), ctypes.c_float(cap), _stream()), "softcap")
+    return z
+
+
+def act_mul(gu: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(gu[:, :I]) * gu[:, I:]; gu [T, 2I], out [T, I], same dtype; kind one of ACTIVATIONS."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"act_mul: {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    _req(gu, "gu", dims=2); _req(out, "out", gu.dtype, 2)
+    if gu.shape[1] != 2 * out.shape[1] or gu.shape[0] != out.shape[0]:
+        raise KernelError("act_mul: gu is not [tokens, 2 * intermediate]")
+    _check(lib().vk_act_mul(_p(gu), _p(out), out.shape[0], out.shape[1], ACTIVATIONS[kind], _dt(gu), _stream()), "act_mul")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Latent attention: what lies around its products and the attention itself
+# ---------------------------------------------------------------------------
+
+def latent_prepare(proj: torch.Tensor, q_rank: int, q_norm_w: torch.Tensor, cq: torch.Tensor, eps: float, positions: torch.Tensor,
+                   freq: torch.Tensor, mag: float, dims: int, interleaved: bool, *, kv_off: int = -1, kv_rank: int = 0, rot_dim: int = 0,
+                   kv_norm_w: Optional[torch.Tensor] = None, slot_mapping: Optional[torch.Tensor] = None,
+                   cache_layer: Optional[torch.Tensor] = None, page_size: int = 0) -> torch.Tensor:
+    """From the float32 rows of the first product: the normed query latent to cq (compute dtype) and, with kv_off >= 0 and a
+    cache layer, the normed key-value latent and the rotated shared key part into the tokens' cache slots
+    (a page: [page_size][kv_rank + rot_dim] keys, then [page_size][kv_rank] values)."""
+    _req(proj, "proj", torch.float32, 2); _req(q_norm_w, "q_norm_w", torch.float32, 1); _req(cq, "cq", dims=2)
+    _req(positions, "positions", torch.int32, 1); _req(freq, "freq", torch.float32, 1)
+    T, N = proj.shape
+    if cq.shape != (T, q_rank) or q_norm_w.shape[0] != q_rank or positions.shape[0] < T or freq.shape[0] * 2 != dims:
+        raise KernelError("latent_prepare: shapes do not fit")
+    write = kv_off >= 0 and cache_layer is not None
+    if write:
+        _req(kv_norm_w, "kv_norm_w", torch.float32, 1); _req(slot_mapping, "slot_mapping", torch.int32, 1)
+        _req(cache_layer, "cache_layer", cq.dtype)
+        if (kv_norm_w.shape[0] != kv_rank or slot_mapping.shape[0] < T
+                or _page_size_of(cache_layer, 1, kv_rank + rot_dim, kv_rank) != page_size):
+            raise KernelError("latent_prepare: the cache layer does not fit the latent's sizes")
+    _check(lib().vk_latent_prepare(_p(proj), N, q_rank, _p(q_norm_w), _p(cq), kv_off if write else -1, kv_rank, rot_dim,
+                                   _p(kv_norm_w if write else None), ctypes.c_float(eps), _p(positions), _p(freq), ctypes.c_float(mag), dims,
+                                   int(bool(interleaved)), _p(slot_mapping if write else None), _p(cache_layer if write else None),
+                                   page_size, T, _dt(cq), _stream()), "latent_prepare")
+    return cq
+
+
+def latent_rotate_q(q: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor, mag: float, heads: int, lat: int, rot_dim: int, dims: int,
+                    interleaved: bool) -> torch.Tensor:
+    """Rotates the first `dims` of the last rot_dim values of every head of q [T, heads * (lat + rot_dim)], in place."""
+    _req(q, "q", dims=2); _req(positions, "positions", torch.int32, 1); _req(freq, "freq", torch.float32, 1)
+    if q.shape[1] != heads * (lat + rot_dim) or positions.shape[0] < q.shape[0] or freq.shape[0] * 2 != dims:
+        raise KernelError("latent_rotate_q: shapes do not fit")
+    _check(lib().vk_latent_rotate_q(_p(q), _p(positions), _p(freq), ctypes.c_float(mag), q.shape[0], heads, lat, rot_dim, dims,
+                                    int(bool(interleaved)), _dt(q), _stream()), "latent_rotate_q")
+    return q
+
+
+def head_gate(x: torch.Tensor, gates: torch.Tensor, off: int, heads: int) -> torch.Tensor:
+    """x [T, heads * d] in place: head h of token t times sigmoid(gates[t, off + h]); gates float32 [T, N]."""
+    _req(x, "x", dims=2); _req(gates, "gates", torch.float32, 2)
+    if x.shape[1] % heads or gates.shape[0] != x.shape[0] or off + heads > gates.shape[1]:
+        raise KernelError("head_gate: shapes do not fit")
+    _check(lib().vk_head_gate(_p(x), _p(gates), gates.shape[1], off, x.shape[0], heads, x.shape[1] // heads, _dt(x), _stream()), "head_gate")
+    return x
+
+
+# ---------------------------------------------------------------------------
+# The gated delta rule with a decay per head and key channel
+# ---------------------------------------------------------------------------
+
+def channel_delta_prep_width(G: int, H: int, dk: int, dv: int) -> int:
+    """Floats of a row of scratch between the kernels: q | k | v | log decay [H dk] | beta [H] | gate [H dv], padded to four."""
+    return (2 * G * dk + 2 * H * dv + H * dk + H + 3) // 4 * 4
+
+
+def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, a2t: torch.Tensor,
+                       g2t: torch.Tensor, norm_w: torch.Tensor, eps: float, token_seg: torch.Tensor, seg_starts: torch.Tensor,
+                       seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor, o: torch.Tensor, out: torch.Tensor, G: int, H: int,
+                       dk: int, dv: int, taps: int) -> torch.Tensor:
+    """The delta rule whose decay differs by head and key channel, from the projections to the input of the output projection.
+    proj float32 [T, 2 G dk + H dv + H + ra + rg] = q | k | v | b | a1 | g1;  a2t float32 [ra, H dk] and g2t [rg, H dv], the wide
+    halves of the two low-rank projections, transposed;  dt_bias [H dk];  a_log [H];  norm_w [dv];  state float32
+    [slots, delta_state_floats];  prep [T, channel_delta_prep_width] and o [T, H dv] float32 scratch;  out [T, H dv] in the compute
+    dtype.  Three launches: prepare, recurrence (which also writes the state), gate."""
+    C = 2 * G * dk + H * dv
+    for name, t, d in (("proj", proj, 2), ("conv_w", conv_w, 2), ("a_log", a_log, 1), ("dt_bias", dt_bias, 1), ("a2t", a2t, 2), ("g2t", g2t, 2),
+                       ("norm_w", norm_w, 1), ("state", state, 2), ("prep", prep, 2), ("o", o, 2)):
+        _req(t, name, torch.float32, d)
+    _req(out, "out", dims=2)
+    _req(token_seg, "token_seg", torch.int32, 1); _req(seg_starts, "seg_starts", torch.int32, 1); _req(seg_slots, "seg_slots", torch.int32, 1)
+    T, S = proj.shape[0], seg_slots.shape[0]
+    ra, rg = a2t.shape[0], g2t.shape[0]
+    if (proj.shape[1] != C + H + ra + rg or conv_w.shape != (C, taps) or a_log.shape[0] != H or dt_bias.shape[0] != H * dk
+            or a2t.shape[1] != H * dk or g2t.shape[1] != H * dv or norm_w.shape[0] != dv
+            or prep.shape != (T, channel_delta_prep_width(G, H, dk, dv)) or o.shape != (T, H * dv) or out.shape != (T, H * dv)
+            or state.shape[1] != delta_state_floats(G, H, dk, dv, taps) or token_seg.shape[0] != T or seg_starts.shape[0] != S + 1):
+        raise KernelError("channel_delta_rule: shapes do not fit the head counts")
+    stride = ctypes.c_size_t(state.stride(0))
+    _check(lib().vk_cdelta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(a2t), _p(g2t), _p(token_seg), _p(seg_starts), _p(seg_slots),
+                                   _p(state), stride, _p(prep), T, G, H, dk, dv, taps, ra, rg, _stream()), "cdelta_prepare")
+    _check(lib().vk_cdelta_recurrence(_p(prep), _p(proj), proj.shape[1], _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, T, G, H, dk,
+                                      dv, taps, _stream()), "cdelta_recurrence")
+    _check(lib().vk_cdelta_gate(_p(o), _p(prep), _p(norm_w), ctypes.c_float(eps), _p(out), T, G, H, dk, dv, _dt(out), _stream()), "cdelta_gate")
+    return out
+
+
+def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, gu: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """out = act(x @ w_gate.T) * (x @ w_up.T) for the two matrices stacked by rows; gu [T, 2I] is scratch in x's dtype."""
+    return act_mul(linear(x, w_gate_up, gu, LINEAR_SAME), out, kind)

@@ -69,3 +69,56 @@ class GatedDeltaRule(Mixer):
                              self.G, self.H, self.dk, self.dv, self.taps, chunk_scratch=scratch,
                              single_tokens=ctx.decode_only and not (ctx.dtype == torch.float32 and ops.float32_exact()))
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
+
+
+class ChannelDeltaRule(Mixer):
+    """The delta rule whose decay differs by head AND key channel, behind two low-rank projections:
+
+        q, k, v, beta   as in GatedDeltaRule
+        decay   = exp(-exp(A_log[h]) * softplus(W_a2 (W_a1 xn) + dt_bias))      [H, dk]: the rows of S decay at rates of their own
+        per head, token after token:   S <- diag(decay) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+        out     = W_o (o / rms(o) * w_norm * sigmoid(W_g2 (W_g1 xn)))
+
+    ONE product makes q | k | v | b | W_a1 xn | W_g1 xn with float32 results; the wide halves W_a2 and W_g2 are applied in float32
+    inside the kernel that prepares the recurrence.  The state and its slot are GatedDeltaRule's."""
+
+    def __init__(self, hidden: int, num_heads: int, num_key_heads: int, key_dim: int, value_dim: int, taps: int, w_in: torch.Tensor,
+                 conv: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, w_a2: torch.Tensor, w_g2: torch.Tensor,
+                 norm_weight: torch.Tensor, wo: torch.Tensor, eps: float):
+        """w_in: q | k | v | b | a1 | g1 stacked by rows ([2 G dk + H dv + H + ra + rg, hidden], compute dtype); w_a2 [H dk, ra] and
+        w_g2 [H dv, rg] (kept in float32, transposed); conv float32 [2 G dk + H dv, taps]; dt_bias [H dk]."""
+        if num_heads % num_key_heads:
+            raise ValueError("value heads do not divide into key heads")
+        H, G, dk, dv = num_heads, num_key_heads, key_dim, value_dim
+        C = 2 * G * dk + H * dv
+        if w_a2.dim() != 2 or w_g2.dim() != 2 or w_a2.shape[0] != H * dk or w_g2.shape[0] != H * dv:
+            raise ValueError("the delta rule's low-rank projections do not fit the head counts")
+        ra, rg = w_a2.shape[1], w_g2.shape[1]
+        if w_in.shape != (C + H + ra + rg, hidden) or conv.shape != (C, taps) or wo.shape != (hidden, H * dv):
+            raise ValueError("the delta rule's weights do not fit the head counts")
+        if a_log.shape != (H,) or dt_bias.shape != (H * dk,) or norm_weight.shape != (dv,):
+            raise ValueError("the delta rule's per-head vectors do not fit the head counts")
+        self.hidden, self.H, self.G, self.dk, self.dv, self.taps, self.eps = hidden, H, G, dk, dv, int(taps), float(eps)
+        self.w_in, self.wo = w_in.contiguous(), wo.contiguous()
+        f32 = lambda t: t.to(torch.float32).contiguous()
+        self.conv, self.a_log, self.dt_bias, self.norm_weight = f32(conv), f32(a_log), f32(dt_bias), f32(norm_weight)
+        self.a2t, self.g2t = f32(w_a2.to(torch.float32).t()), f32(w_g2.to(torch.float32).t())
+
+    def tensors(self):
+        return [self.w_in, self.conv, self.a_log, self.dt_bias, self.a2t, self.g2t, self.norm_weight, self.wo]
+
+    def cache_spec(self):
+        return StateSpec((ops.delta_state_floats(self.G, self.H, self.dk, self.dv, self.taps),), torch.float32)
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor, write_cache: bool = True,
+                norm=None) -> None:
+        if not write_cache:
+            raise ValueError("a recurrent mixer has no cache that another run could read")
+        T, ws = ctx.num_tokens, ctx.workspace
+        proj = ops.linear(xn, self.w_in, ws.rows("cdelta.proj", T, self.w_in.shape[0], torch.float32), ops.LINEAR_F32)
+        out = ops.channel_delta_rule(proj, self.conv, self.a_log, self.dt_bias, self.a2t, self.g2t, self.norm_weight, self.eps, ctx.token_seg,
+                                     ctx.seg_starts, ctx.seg_slots, cache.state,
+                                     ws.rows("cdelta.prep", T, ops.channel_delta_prep_width(self.G, self.H, self.dk, self.dv), torch.float32),
+                                     ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
+                                     self.G, self.H, self.dk, self.dv, self.taps)
+        ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)

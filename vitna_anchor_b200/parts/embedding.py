@@ -28,6 +28,25 @@ class Embedding(TokenInput):
         return ops.embed_rows(self.table, ctx.tokens, x)
 
 
+class NormedEmbedding(Embedding):
+    """x = norm(the token's row): the rows are normed in float32 where they lie.  `norm` is any norm with in_place()."""
+
+    def __init__(self, vocab: int, hidden: int, table: torch.Tensor, norm):
+        super().__init__(vocab, hidden, table)
+        if not hasattr(norm, "in_place"):
+            raise ValueError("the embedding's norm cannot norm float32 rows in place")
+        self.norm = norm
+
+    def tensors(self):
+        return [self.table] + self.norm.tensors()
+
+    def weight_bytes(self) -> int:
+        return self.norm.weight_bytes()         # a row per token is read, not the table
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        return self.norm.in_place(super().forward(ctx))
+
+
 class ScaledEmbedding(TokenInput):
     """x = scale * the token's row + a learned row for the token's position (unscaled), written `copies` times side by
     side: float32 [T, copies * hidden], the form a model with several residual streams starts from."""
@@ -79,3 +98,19 @@ class LMHead(LogitsOutput):
         """logits of rmsnorm(x[rows]) in one launch (few rows); x is the float32 residual stream."""
         nw, eps = norm.as_rms()
         return ops.linear_skinny(x, self.weight, self._out(rows.shape[0], out, x.device), ops.EPI_F32, norm_weight=nw, eps=eps, rows=rows)
+
+
+class CappedLMHead(LMHead):
+    """logits <- cap * tanh(logits / cap) after the output matrix (float32, in place)."""
+
+    def __init__(self, vocab: int, hidden: int, weight: torch.Tensor, cap: float):
+        super().__init__(vocab, hidden, weight)
+        if not cap > 0:
+            raise ValueError("the soft cap of the logits is positive")
+        self.cap = float(cap)
+
+    def forward(self, xn: torch.Tensor, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.softcap(super().forward(xn, ctx, out), self.cap)
+
+    def forward_normed(self, x: torch.Tensor, rows: torch.Tensor, norm, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.softcap(super().forward_normed(x, rows, norm, ctx, out), self.cap)

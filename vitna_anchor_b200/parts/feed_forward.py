@@ -2,6 +2,8 @@
 (engine/src/model.c:962-972; silu(g) = g / (1 + exp(-g)), engine/src/ops.c:283-288).
 The gate and up matrices are stacked by rows so that one product reads xn once.
 
+With another activation than silu (`activation`, one of ops.ACTIVATIONS) it is the same gated form, y = W_down (act(W_gate xn) * (W_up xn)).
+
 The dense feed-forward: y = W_down act(W_up xn), act one of ops.ACTIVATIONS (the erf or the tanh form of gelu, silu)."""
 from __future__ import annotations
 
@@ -12,23 +14,28 @@ from .base import FeedForward, StepContext
 
 
 class SwiGLU(FeedForward):
-    def __init__(self, hidden: int, intermediate: int, w_gate_up: torch.Tensor, w_down: torch.Tensor):
+    def __init__(self, hidden: int, intermediate: int, w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str = "silu"):
         if w_gate_up.shape != (2 * intermediate, hidden) or w_down.shape != (hidden, intermediate):
             raise ValueError("feed-forward weights do not fit the sizes")
-        self.hidden, self.intermediate = hidden, intermediate
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} is not one of {sorted(ops.ACTIVATIONS)}")
+        self.hidden, self.intermediate, self.activation = hidden, intermediate, activation
         self.w_gate_up, self.w_down = w_gate_up.contiguous(), w_down.contiguous()
 
     def tensors(self):
         return [self.w_gate_up, self.w_down]
 
     def fuses_norm(self, norm, ctx: StepContext) -> bool:
-        return norm.as_rms() is not None and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate)
+        return (self.activation == "silu" and norm.as_rms() is not None
+                and ops.fused_norm_takes(ctx.dtype, ctx.num_tokens, self.hidden, 2 * self.intermediate))
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, residual: torch.Tensor, norm=None) -> None:
         T = ctx.num_tokens
         ws = ctx.workspace
         act_buf = ws.rows("ffn.act", T, self.intermediate, ctx.dtype)
-        if norm is not None:
+        if self.activation != "silu":
+            act = ops.linear_gated(xn, self.w_gate_up, ws.rows("ffn.gu", T, 2 * self.intermediate, ctx.dtype), act_buf, self.activation)
+        elif norm is not None:
             # few rows: norm, gate and up, and silu(gate) * up in one launch
             nw, eps = norm.as_rms()
             act = ops.linear_skinny(xn, self.w_gate_up, act_buf, ops.EPI_SWIGLU, norm_weight=nw, eps=eps)

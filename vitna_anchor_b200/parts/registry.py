@@ -33,16 +33,21 @@ def make_part(kind: str, name: str, **params):
 def _register_builtin() -> None:
     from .attention import PagedAttention
     from .block import PreNormBlock
-    from .delta import GatedDeltaRule
+    from .delta import ChannelDeltaRule, GatedDeltaRule
+    from .latent import LatentAttention
     from .feed_forward import DenseMLP, SwiGLU
     from .hyper import HyperBlock
-    from .norms import RMSNorm
+    from .norms import LayerNorm, RMSNorm
     from .rotary import NoPositionEncoding, Rotary
     register_part("mixer", "attention", PagedAttention)
     register_part("mixer", "gated_delta", GatedDeltaRule)
+    register_part("mixer", "channel_delta", ChannelDeltaRule)
+    register_part("mixer", "latent_attention", LatentAttention.from_matrices)
     register_part("feed_forward", "swiglu", SwiGLU)
+    register_part("feed_forward", "gated", SwiGLU)           # the same part; `activation` chooses the gate's function
     register_part("feed_forward", "dense", DenseMLP)
     register_part("norm", "rmsnorm", RMSNorm)
+    register_part("norm", "layernorm", LayerNorm)
     register_part("position", "rotary", Rotary)
     register_part("position", "none", NoPositionEncoding)
     register_part("block", "pre_norm", PreNormBlock)

@@ -35,3 +35,25 @@ class Rotary(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     """Nothing is added or rotated."""
+
+
+def blended_frequencies(base: float, dims: int, scaling=None):
+    """Frequencies of a rotation over `dims` values, f_i = base^(-2i/dims), i < dims/2, and the factor on cos and sin.
+
+    With scaling = (factor, original, fast, slow) the frequencies of long wavelengths are divided by `factor` and those of
+    short ones kept, with a linear ramp over i between them (the YaRN recipe): with
+    at(turns) = dims * ln(original / (2 pi turns)) / (2 ln base),  lo = max(floor(at(fast)), 0),  hi = min(ceil(at(slow)), dims - 1),
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)  the frequency is  f_i / factor * ramp_i + f_i * (1 - ramp_i),  and cos
+    and sin are multiplied by 0.1 ln(factor) + 1.  Worked out in float64 on the host; -> (float32 [dims/2] array, float)."""
+    import math
+    if dims % 2:
+        raise ValueError("a rotation turns an even number of values")
+    i = np.arange(dims // 2, dtype=np.float64)
+    f = np.power(float(base), -2.0 * i / dims)
+    if scaling is None:
+        return f.astype(np.float32), 1.0
+    factor, original, fast, slow = (float(v) for v in scaling)
+    at = lambda turns: dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(base)))
+    lo, hi = max(math.floor(at(fast)), 0), min(math.ceil(at(slow)), dims - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32), 0.1 * math.log(factor) + 1.0
