@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--model 135M|360M|1.7B] [--workload decode|mixed|prefill8k|lupanex]
+                    [--model 135M|360M|1.7B] [--workload decode|mixed|prefill8k|lupanex|siparax]
 
 The default run is SmolLM2-135M's sizes with random weights (N(0, 0.02), norm weights 1, seed 0) in
 bfloat16, a batch of 8 requests each decoding from its own 2,048-token random prompt, cache context
@@ -22,6 +22,10 @@ most 512 tokens beside the decoded tokens of the others, 128 new tokens each, th
 streams, dense gelu feed-forward) at two sets of layer sizes, random weights, beside a Llama model of the same width, depth and
 number of weights: a 2,048-token prompt and batch-8 decoding from 2,048-token prompts for both, and where a prompt's time goes,
 kind of kernel by kind of kernel, against each kind's own roofline (LUPANEX_SIZES below).
+--workload siparax: the Siparax design (latent attention beside the delta rule with a decay per key channel, layer norms, gated
+gelu feed-forward) at two sets of layer sizes, random weights, beside a Lupanex model (its closest relative here: attention and
+the gated delta rule in the same order of layers, one residual stream) of the same width, depth and number of feed-forward
+weights: the same measurements as --workload lupanex (SIPARAX_SIZES below).
 --workload prefill8k: one 8,192-token prompt, in one step and in portions of 2,048 through the scheduler.
 
 --impl reference builds nothing of this repository's engine: it runs the unmodified reference program
@@ -525,9 +529,9 @@ def kind_of(launch):
         return "product"
     if launch.startswith("attention"):
         return "attention"
-    if launch.startswith("delta"):
+    if launch.startswith(("delta", "cdelta")):
         return "delta"
-    if launch in ("hyper_step", "rmsnorm_rows"):
+    if launch in ("hyper_step", "rmsnorm_rows", "layernorm_rows", "act_mul", "latent_prepare", "latent_rotate_q", "head_gate", "qk_norm_store"):
         return "between"
     return "other"
 
@@ -562,6 +566,89 @@ def prompt_by_kind(model, work, pk, tokens=PREFILL_TOKENS):
     return {"kinds": out, "launches": launches}
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --workload siparax
+# ---------------------------------------------------------------------------------------------------------------
+
+# The same two sets of sizes; three of four layers are delta layers, the fourth is latent attention whose cached row (the
+# key-value latent and the shared rotated part) is 128 values a token.  The gated feed-forward is two thirds as wide as
+# Lupanex's dense one, which gives both the same number of weights.
+SIPARAX_SIZES = {
+    "w576": dict(width=576, ff=1536, heads=9, kv=3, dim=64, vdim=64, layers=12, rot_dim=32, kv_rank=96, q_rank=192, lupanex_ff=2304),
+    "w2048": dict(width=2048, ff=8192, heads=16, kv=4, dim=128, vdim=128, layers=8, rot_dim=32, kv_rank=96, q_rank=512, lupanex_ff=12288),
+}
+SIPARAX_RANK = 16           # what random initialisation takes for the ranks of the delta rule's low-rank projections
+
+
+def siparax_config(sz):
+    rot = dict(base=10000.0, dims=sz["rot_dim"], scaling=dict(factor=8.0, original=2048, fast=32.0, slow=1.0))
+    att = dict(heads=sz["heads"], dim=sz["dim"], rot_dim=sz["rot_dim"], vdim=sz["vdim"], kv_rank=sz["kv_rank"], q_rank=sz["q_rank"],
+               scale=(sz["dim"] + sz["rot_dim"]) ** -0.5, rot=rot)
+    dl = dict(heads=sz["heads"], kv_heads=sz["kv"], dim=sz["dim"], vdim=sz["vdim"], conv=4)
+    mlp = dict(kind="dense", ff=sz["ff"])
+    layers = [dict(type="latent_attention_2" if i % 4 == 3 else "channel_delta", mixer=att if i % 4 == 3 else dl, mlp=mlp)
+              for i in range(sz["layers"])]
+    return dict(architecture="Siparax", vocab=LUPANEX_VOCAB, width=sz["width"], norm=dict(eps=1e-6), logit_softcap=30.0, layers=layers)
+
+
+def lupanex_plain_config(sz):
+    """Lupanex with one residual stream: the same order of layers, head counts and sizes."""
+    c = lupanex_config(dict(sz, ff=sz["lupanex_ff"]))
+    del c["streams"]
+    return c
+
+
+def siparax_work(sz, T):
+    """Algorithmic work of one T-token prompt, by kind of kernel: (flops, bytes)."""
+    W, L = sz["width"], sz["layers"]
+    n_att = L // 4
+    n_delta = L - n_att
+    H, G, dk, dv, r = sz["heads"], sz["kv"], sz["dim"], sz["vdim"], SIPARAX_RANK
+    hd, vd = sz["kv_rank"] + sz["rot_dim"], sz["kv_rank"]
+    att_w = W * (sz["q_rank"] + hd + H) + sz["q_rank"] * H * hd + H * vd * W          # the folded query and output matrices
+    delta_rows = 2 * G * dk + H * dv + H + 2 * r
+    products = 2.0 * T * (n_att * att_w + n_delta * W * (delta_rows + H * dv) + L * 3 * W * sz["ff"])
+    prep = 2 * G * dk + 2 * H * dv + H * dk + H
+    return {
+        "product": (products, 0.0),
+        "attention": (n_att * float(T) * (T + 1) * H * (hd + vd), 0.0),
+        "delta": (n_delta * T * (6.0 * H * dk * dv + 2.0 * r * H * (dk + dv)), n_delta * T * 4.0 * (delta_rows + 2 * prep + 2 * H * dv)),
+        "between": (0.0, (2 * L + 2) * T * W * 6.0 + L * T * sz["ff"] * 6.0 + n_att * T * (4.0 * (sz["q_rank"] + hd) + 6.0 * H * hd)),
+    }
+
+
+def lupanex_plain_work(sz, T):
+    w = lupanex_work(dict(sz, ff=sz["lupanex_ff"]), T)
+    w["between"] = (0.0, (2 * sz["layers"] + 1) * T * sz["width"] * 6.0)
+    return w
+
+
+def siparax_run(a, pk, clocks):
+    import torch
+    from vitna_anchor_b200.engine.loading import random_model_on_device
+    results = {}
+    for name, sz in SIPARAX_SIZES.items():
+        row = {}
+        for which, cfg, work in (("siparax", siparax_config(sz), siparax_work(sz, PREFILL_TOKENS)),
+                                 ("lupanex", lupanex_plain_config(sz), lupanex_plain_work(sz, PREFILL_TOKENS))):
+            model = random_model_on_device(cfg, 0)
+            if model.max_positions > CONTEXT:
+                model.max_positions = CONTEXT           # the design has no limit of its own; the run's cache has
+            pf = prefill_run(model, None, clocks, repeats=3)
+            dec = decode_run(model, a.batch, min(a.steps, 32), a.warmup, clocks, with_e2e=False)
+            flops = sum(f for f, _ in work.values())
+            row[which] = {"weights_mb": round(model.step_weight_bytes() / 1e6, 1),
+                          "prefill_2048": {"tokens_per_s": round(pf["value"]), "ms": round(pf["ms"], 3),
+                                           "frac_bf16": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                          f"decode_b{a.batch}": {"tokens_per_s": round(dec["value"]), "ms_per_step": round(dec["ms_per_step"], 4),
+                                                 "frac_hbm": round(dec["gbs"] / pk["hbm_gbs"], 4), "launches_per_step": dec["launches"] // min(a.steps, 32)},
+                          "prompt_by_kind": prompt_by_kind(model, work, pk)}
+            del model
+            torch.cuda.empty_cache()
+        results[name] = row
+    return results
+
+
 def lupanex_run(a, pk, clocks):
     import torch
     from vitna_anchor_b200.engine.loading import random_model_on_device
@@ -593,7 +680,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="135M", choices=sorted(MODELS), help="layer sizes: SmolLM2-135M (the default), 360M or 1.7B")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "prefill8k", "lupanex", "siparax"],
                     help="decode (the default line), mixed (32 requests, 512-token portions beside decodes), prefill8k, lupanex "
                          "(the Lupanex design beside a Llama model of equal size)")
     ap.add_argument("--no-points", action="store_true", help="skip the other batches, models and the prefill")
@@ -631,6 +718,15 @@ def main():
                           f"batch-{a.batch} decoding from 2,048-token prompts; a prompt's time by kind of kernel against its roofline",
                           "impl": "ours", "dtype": "bf16", "data": "synthetic: random weights drawn on the device, uniform-random token ids",
                           "peaks": pk, "sizes": r, "clocks": clocks.summary()}))
+        return 0
+    if a.workload == "siparax":
+        r = siparax_run(a, pk, clocks)
+        clocks.stop()
+        print(json.dumps({"metric": "Siparax beside Lupanex (one residual stream) at equal width, depth and feed-forward weights: tokens/s of a "
+                          f"2,048-token prompt and of batch-{a.batch} decoding from 2,048-token prompts; a prompt's time by kind of kernel "
+                          "against its roofline", "impl": "ours", "dtype": "bf16",
+                          "data": "synthetic: random weights drawn on the device, uniform-random token ids", "peaks": pk, "sizes": r,
+                          "clocks": clocks.summary()}))
         return 0
     if a.workload == "mixed":
         model = random_model_on_device(config_json(SIZES), 0) if a.model != "135M" else model_folder()

@@ -17,8 +17,9 @@
 //     and then, for t = 1..M, no further sum over dk:
 //         u_t = beta_t (v_t - D_t);   D_j += A[t][j] u_t (j > t);   E_j += B[t][j] u_t (j >= t);   o_t = E_t
 //         A[t][j] = sum_d k_t[d] k_j[d] e^{L_j[d] - L_t[d]},   B[t][j] = sum_d k_t[d] q_j[d] e^{L_j[d] - L_t[d]}
-//     and S <- diag(e^{L_M}) S + sum_t (e^{L_M - L_t} k_t) u_t^T.  Every exponent is <= 0.  The block works out A, B and the scaled
-//     vectors once per chunk for all its columns.  M = 1 is the plain recurrence (single decoded tokens).
+//     and S <- diag(e^{L_M}) S + sum_t (e^{L_M - L_t} k_t) u_t^T.  Every exponent is <= 0.  A, B and the scaled vectors are worked out
+//     vectors in a kernel of its own for all groups side by side (a warp a token and head), so that the chain from token to token
+//     holds no exponential and no sum over dk beyond the 2M above.  M = 1 is the plain recurrence (single decoded tokens).
 //  3. gate: o / rms(o) over dv, times a weight shared by the heads, times the gate of 1, in the compute dtype.
 //
 // Everything is float32.  A request's state row is the other form's: [H*dv*dk floats of S^T][(taps-1)*C convolution inputs].
@@ -29,76 +30,163 @@ namespace vk {
 // prep row: q | k | v | log decay (H*dk) | beta (H) | gate (H*dv)
 __host__ __device__ inline int cd_prep_width(int G, int H, int dk, int dv) { return (2 * G * dk + 2 * H * dv + H * dk + H + 3) / 4 * 4; }
 
-// One block per token.  smem: act [C], a1 [ra], g1 [rg].
+// A block takes TOK consecutive tokens: per token the convolution, unit lengths and beta, then for all of them at once the wide
+// halves of the two low-rank projections, so that a value of a2 or g2 is fetched once for TOK tokens (a prompt's launch; a step
+// of few tokens takes TOK = 1 and as many blocks as tokens).  smem: act [C], then a1 | g1 of every token [TOK][ra + rg].
+template <int TOK>
 __global__ void __launch_bounds__(1024) cdelta_prepare_kernel(
     const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
     const float* __restrict__ a2t, const float* __restrict__ g2t, const int32_t* __restrict__ token_seg, const int32_t* __restrict__ seg_starts,
     const int32_t* __restrict__ seg_slots, const float* __restrict__ state, size_t state_stride, size_t conv_off, float* __restrict__ prep,
-    int P, int G, int H, int dk, int dv, int taps, int ra, int rg) {
+    int P, int tokens, int G, int H, int dk, int dv, int taps, int ra, int rg) {
     extern __shared__ float act[];
     dependency_wait();
     let_dependents_start();
-    const int t = blockIdx.x, tid = threadIdx.x;
-    const int C = 2 * G * dk + H * dv, N = C + H + ra + rg;
-    float* lr = act + C;                                     // a1, then g1
-    const int seg = token_seg[t];
-    const int i = t - seg_starts[seg];
-    const int slot = seg_slots[seg];
-    const float* old = slot >= 0 ? state + (size_t)slot * state_stride + conv_off : nullptr;   // [taps-1][C]
-    const float* in = proj + (size_t)t * N;
-    for (int c = tid; c < C; c += blockDim.x) {
-        float x[DR_MAX_TAPS], w[DR_MAX_TAPS];
+    const int tid = threadIdx.x;
+    const int C = 2 * G * dk + H * dv, N = C + H + ra + rg, LR = ra + rg;
+    float* lr = act + C;                                     // [TOK][a1 | g1]
+    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+    const int tb = blockIdx.x * TOK;
+    for (int k = 0; k < TOK; k++) {
+        const int t = tb + k;
+        if (t >= tokens) break;
+        const int seg = token_seg[t];
+        const int i = t - seg_starts[seg];
+        const int slot = seg_slots[seg];
+        const float* old = slot >= 0 ? state + (size_t)slot * state_stride + conv_off : nullptr;   // [taps-1][C]
+        const float* in = proj + (size_t)t * N;
+        for (int c = tid; c < C; c += blockDim.x) {
+            float x[DR_MAX_TAPS], w[DR_MAX_TAPS];
 #pragma unroll
-        for (int j = 0; j < DR_MAX_TAPS; j++) {
-            if (j < taps) {
-                const int src = i - j;
-                x[j] = src >= 0 ? proj[(size_t)(t - j) * N + c] : (old ? old[(size_t)(taps - 1 + src) * C + c] : 0.0f);
-                w[j] = conv_w[(size_t)c * taps + (taps - 1 - j)];
+            for (int j = 0; j < DR_MAX_TAPS; j++) {
+                if (j < taps) {
+                    const int src = i - j;
+                    x[j] = src >= 0 ? proj[(size_t)(t - j) * N + c] : (old ? old[(size_t)(taps - 1 + src) * C + c] : 0.0f);
+                    w[j] = conv_w[(size_t)c * taps + (taps - 1 - j)];
+                }
+            }
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = DR_MAX_TAPS - 1; j >= 0; j--)      // oldest input first
+                if (j < taps) acc = fmaf(w[j], x[j], acc);
+            act[c] = silu_f(acc);
+        }
+        for (int r = tid; r < LR; r += blockDim.x) lr[k * LR + r] = in[C + H + r];
+        __syncthreads();
+        float* out = prep + (size_t)t * P;
+        for (int hq = warp; hq < 2 * G; hq += nwarps) {      // q heads, then k heads
+            const float* v = act + (size_t)hq * dk;
+            float ss = 0.0f;
+            for (int d = lane; d < dk; d += 32) ss = fmaf(v[d], v[d], ss);
+            ss = warp_sum(ss);
+            float inv = 1.0f / sqrtf(ss + 1e-6f);
+            if (hq < G) inv *= 1.0f / sqrtf((float)dk);
+            for (int d = lane; d < dk; d += 32) out[(size_t)hq * dk + d] = v[d] * inv;
+        }
+        for (int c = 2 * G * dk + tid; c < C; c += blockDim.x) out[c] = act[c];
+        for (int h = tid; h < H; h += blockDim.x) out[C + (size_t)H * dk + h] = sigmoid_f(in[C + h]);
+        __syncthreads();                                     // act is written again for the next token
+    }
+    const int HK = H * dk, HV = H * dv;
+    const int nt = tokens - tb < TOK ? tokens - tb : TOK;
+    for (int c = tid; c < HK; c += blockDim.x) {             // the decay's logarithm; the recurrence takes exp of sums of it
+        float acc[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; k++) acc[k] = 0.0f;
+        for (int r = 0; r < ra; r++) {
+            const float w = a2t[(size_t)r * HK + c];
+#pragma unroll
+            for (int k = 0; k < TOK; k++) acc[k] = fmaf(w, lr[k * LR + r], acc[k]);
+        }
+        const float rate = -expf(a_log[c / dk]), bias = dt_bias[c];
+#pragma unroll
+        for (int k = 0; k < TOK; k++)
+            if (k < nt) prep[(size_t)(tb + k) * P + C + c] = rate * softplus_f(acc[k] + bias);
+    }
+    for (int c = tid; c < HV; c += blockDim.x) {
+        float acc[TOK];
+#pragma unroll
+        for (int k = 0; k < TOK; k++) acc[k] = 0.0f;
+        for (int r = 0; r < rg; r++) {
+            const float w = g2t[(size_t)r * HV + c];
+#pragma unroll
+            for (int k = 0; k < TOK; k++) acc[k] = fmaf(w, lr[k * LR + ra + r], acc[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < TOK; k++)
+            if (k < nt) prep[(size_t)(tb + k) * P + C + HK + H + c] = sigmoid_f(acc[k]);
+    }
+}
+
+// What the recurrence needs of a group of M tokens and does not depend on the state, for all groups side by side: a warp per
+// (token, head).  A token's group is the M tokens from the last multiple of M before its place in this step's portion of its
+// request (the last group of a portion may be shorter).  Row (t, h) of `grp`, GW = 4 * dkr + 8 floats (dkr = dk rounded up to a
+// multiple of four; the padding is zero):
+//     e^{L_t} k_t | e^{L_t} q_t | e^{L_last - L_t} k_t | e^{L_t} | A[t][0..M-1] | B[t][0..M-1]
+// with L_t the sum of the group's log decays up to and including token t, A[t][j] = sum_d k_t k_j e^{L_j - L_t} for j > t and
+// B[t][j] = sum_d k_t q_j e^{L_j - L_t} for j >= t (zero elsewhere).
+template <int M>
+__global__ void __launch_bounds__(256) cdelta_groups_kernel(const float* __restrict__ prep, int P, const int32_t* __restrict__ token_seg,
+                                                            const int32_t* __restrict__ seg_starts, float* __restrict__ grp, int tokens, int G,
+                                                            int H, int dk, int dv) {
+    dependency_wait();
+    let_dependents_start();
+    const int unit = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= tokens * H) return;
+    const int t = unit / H, h = unit - t * H;
+    const int g = h / (H / G);
+    const int seg = token_seg[t];
+    const int first = seg_starts[seg], i = t - first, n = seg_starts[seg + 1] - first;
+    const int p = i % M, t0 = t - p;
+    const int gl = n - (i - p) < M ? n - (i - p) : M;           // tokens of this group
+    const int C = 2 * G * dk + H * dv, dkr = (dk + 3) / 4 * 4, GW = 4 * dkr + 8;      // eight floats for the products whatever M is: rows stay 16-byte aligned
+    float* out = grp + (size_t)unit * GW;
+    float a[M], b[M];
+#pragma unroll
+    for (int j = 0; j < M; j++) { a[j] = 0.0f; b[j] = 0.0f; }
+    for (int d = lane; d < dkr; d += 32) {
+        if (d >= dk) { out[d] = 0.0f; out[dkr + d] = 0.0f; out[2 * dkr + d] = 0.0f; out[3 * dkr + d] = 0.0f; continue; }
+        float L[M];
+        float run = 0.0f;
+#pragma unroll
+        for (int j = 0; j < M; j++) {
+            if (j < gl) run += prep[(size_t)(t0 + j) * P + C + (size_t)h * dk + d];
+            L[j] = run;
+        }
+        const float lt = L[p], last = L[M - 1];
+        const float kt = prep[(size_t)t * P + (size_t)(G + g) * dk + d], qt = prep[(size_t)t * P + (size_t)g * dk + d];
+        const float et = expf(lt);
+        out[d] = et * kt;
+        out[dkr + d] = et * qt;
+        out[2 * dkr + d] = expf(last - lt) * kt;
+        out[3 * dkr + d] = et;
+#pragma unroll
+        for (int j = 0; j < M; j++) {
+            if (j == p) b[j] = fmaf(kt, qt, b[j]);
+            else if (j > p && j < gl) {
+                const float w = kt * expf(L[j] - lt);
+                a[j] = fmaf(w, prep[(size_t)(t0 + j) * P + (size_t)(G + g) * dk + d], a[j]);
+                b[j] = fmaf(w, prep[(size_t)(t0 + j) * P + (size_t)g * dk + d], b[j]);
             }
         }
-        float acc = 0.0f;
+    }
 #pragma unroll
-        for (int j = DR_MAX_TAPS - 1; j >= 0; j--)          // oldest input first
-            if (j < taps) acc = fmaf(w[j], x[j], acc);
-        act[c] = silu_f(acc);
-    }
-    for (int r = tid; r < ra + rg; r += blockDim.x) lr[r] = in[C + H + r];
-    __syncthreads();
-    float* out = prep + (size_t)t * P;
-    const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-    for (int hq = warp; hq < 2 * G; hq += nwarps) {          // q heads, then k heads
-        const float* v = act + (size_t)hq * dk;
-        float ss = 0.0f;
-        for (int d = lane; d < dk; d += 32) ss = fmaf(v[d], v[d], ss);
-        ss = warp_sum(ss);
-        float inv = 1.0f / sqrtf(ss + 1e-6f);
-        if (hq < G) inv *= 1.0f / sqrtf((float)dk);
-        for (int d = lane; d < dk; d += 32) out[(size_t)hq * dk + d] = v[d] * inv;
-    }
-    for (int c = 2 * G * dk + tid; c < C; c += blockDim.x) out[c] = act[c];
-    const int HK = H * dk, HV = H * dv;
-    for (int c = tid; c < HK; c += blockDim.x) {             // the decay's logarithm; the recurrence takes exp of sums of it
-        float acc = 0.0f;
-        for (int r = 0; r < ra; r++) acc = fmaf(a2t[(size_t)r * HK + c], lr[r], acc);
-        out[C + c] = -expf(a_log[c / dk]) * softplus_f(acc + dt_bias[c]);
-    }
-    for (int h = tid; h < H; h += blockDim.x) out[C + HK + h] = sigmoid_f(in[C + h]);
-    for (int c = tid; c < HV; c += blockDim.x) {
-        float acc = 0.0f;
-        for (int r = 0; r < rg; r++) acc = fmaf(g2t[(size_t)r * HV + c], lr[ra + r], acc);
-        out[C + HK + H + c] = sigmoid_f(acc);
+    for (int j = 0; j < M; j++) { a[j] = warp_sum(a[j]); b[j] = warp_sum(b[j]); }
+    if (lane == 0) {
+#pragma unroll
+        for (int j = 0; j < M; j++) { out[4 * dkr + j] = a[j]; out[4 * dkr + M + j] = b[j]; }
     }
 }
 
 // grid (segments, H, column parts); block = cols * R threads, thread = (column, lane of the column); a lane holds KPT values of
 // its column in pieces of four: piece i of lane r is rows (i*R + r)*4 .. +3 of S (zero beyond dk).
-// One staged buffer: q [chunk][dkp], k [chunk][dkp], l [chunk][dkp] (log decays, then their running sums), kt [chunk][dkp]
-// (e^{L} k), v [chunk][cols], beta [chunk], products [chunk/M][2][M][M].
+// One staged buffer: kt, qt, kf, el [chunk][dkp] each (the four vectors of the groups kernel), v [chunk][cols], beta [chunk],
+// products [chunk][2][M].  Tokens are staged `chunk` at a time by cp.async, a chunk ahead of the arithmetic.
 template <int KPT, int M>
 __global__ void __launch_bounds__(256) cdelta_recurrence_kernel(
-    const float* __restrict__ prep, int P, const float* __restrict__ proj, int N, const int32_t* __restrict__ seg_starts,
-    const int32_t* __restrict__ seg_slots, float* __restrict__ state, size_t state_stride, size_t conv_off, float* __restrict__ o, int G, int H,
-    int dk, int dv, int taps, int R, int cols, int chunk, int vec) {
+    const float* __restrict__ prep, int P, const float* __restrict__ grp, const float* __restrict__ proj, int N,
+    const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots, float* __restrict__ state, size_t state_stride,
+    size_t conv_off, float* __restrict__ o, int G, int H, int dk, int dv, int taps, int R, int cols, int chunk, int vec) {
     extern __shared__ __align__(16) float sm[];
     const int seg = blockIdx.x, h = blockIdx.y, part = blockIdx.z, tid = threadIdx.x;
     dependency_wait();
@@ -107,9 +195,8 @@ __global__ void __launch_bounds__(256) cdelta_recurrence_kernel(
     if (slot < 0) return;                                    // a padding segment of a captured batch
     const int start = seg_starts[seg], n = seg_starts[seg + 1] - start;
     const int C = 2 * G * dk + H * dv;
-    const int g = h / (H / G);
     const int dkp = R * KPT;                                 // dk rounded up to what the lanes hold (a power of two)
-    const int dk4 = dk / 4, dkp4 = dkp / 4;
+    const int dkr = (dk + 3) / 4 * 4, dkr4 = dkr / 4, dkp4 = dkp / 4, GW = 4 * dkr + 8;      // eight floats for the products whatever M is: rows stay 16-byte aligned
     const int sh4 = 31 - __clz(dkp4);
     float* row = state + (size_t)slot * state_stride;
 
@@ -132,51 +219,38 @@ __global__ void __launch_bounds__(256) cdelta_recurrence_kernel(
     }
 
     auto stage = [&](int c0, int b) {
-        float* q_s = sm + b * buf_floats;
-        float* k_s = q_s + chunk * dkp;
-        float* l_s = k_s + chunk * dkp;
-        float* v_s = l_s + 2 * chunk * dkp;
+        float* vec_s = sm + b * buf_floats;                  // kt | qt | kf | el, [chunk][dkp] each
+        float* v_s = vec_s + 4 * chunk * dkp;
         float* b_s = v_s + chunk * cols;
+        float* gram = b_s + chunk;                           // [chunk][2][M]
         const int cn = n - c0 < chunk ? n - c0 : chunk;
-        for (int e = tid; e < cn * dkp4; e += blockDim.x) {
-            const int j = e >> sh4, d4 = e & (dkp4 - 1);
-            const float* p = prep + (size_t)(start + c0 + j) * P;
-            if (!vec) {
-#pragma unroll
-                for (int x = 0; x < 4; x++) {
-                    const int d = d4 * 4 + x;
-                    if (d < dk) {
-                        dr_cp_async4(q_s + e * 4 + x, p + (size_t)g * dk + d);
-                        dr_cp_async4(k_s + e * 4 + x, p + (size_t)(G + g) * dk + d);
-                        dr_cp_async4(l_s + e * 4 + x, p + C + (size_t)h * dk + d);
-                    } else {
-                        q_s[e * 4 + x] = 0.0f;
-                        k_s[e * 4 + x] = 0.0f;
-                        l_s[e * 4 + x] = 0.0f;
-                    }
-                }
-            } else if (d4 < dk4) {
-                dr_cp_async16(q_s + e * 4, p + (size_t)g * dk + d4 * 4);
-                dr_cp_async16(k_s + e * 4, p + (size_t)(G + g) * dk + d4 * 4);
-                dr_cp_async16(l_s + e * 4, p + C + (size_t)h * dk + d4 * 4);
-            } else {
-                *reinterpret_cast<float4*>(q_s + e * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                *reinterpret_cast<float4*>(k_s + e * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                *reinterpret_cast<float4*>(l_s + e * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            }
-        }
-        for (int j = 0; j < cn; j++) {
-            for (int cc = tid; cc < cols; cc += blockDim.x) {
-                const int c = part * cols + cc;
-                if (c < dv) dr_cp_async4(v_s + j * cols + cc, prep + (size_t)(start + c0 + j) * P + 2 * G * dk + (size_t)h * dv + c);
-                else v_s[j * cols + cc] = 0.0f;
-            }
-        }
-        for (int j = tid; j < cn; j += blockDim.x) dr_cp_async4(b_s + j, prep + (size_t)(start + c0 + j) * P + C + (size_t)H * dk + h);
         const int cnp = (cn + M - 1) / M * M;                // tokens that do nothing fill the last group
-        for (int e = cn * dkp + tid; e < cnp * dkp; e += blockDim.x) { q_s[e] = 0.0f; k_s[e] = 0.0f; l_s[e] = 0.0f; }
-        for (int e = cn * cols + tid; e < cnp * cols; e += blockDim.x) v_s[e] = 0.0f;
-        for (int j = cn + tid; j < cnp; j += blockDim.x) b_s[j] = 0.0f;
+        for (int e = tid; e < cnp * dkp4; e += blockDim.x) {
+            const int j = e >> sh4, d4 = e & (dkp4 - 1);
+            if (j < cn && d4 < dkr4) {
+                const float* src = grp + ((size_t)(start + c0 + j) * H + h) * GW + d4 * 4;
+#pragma unroll
+                for (int w = 0; w < 4; w++) dr_cp_async16(vec_s + (w * chunk + j) * dkp + d4 * 4, src + w * dkr);
+            } else {
+#pragma unroll
+                for (int w = 0; w < 4; w++) *reinterpret_cast<float4*>(vec_s + (w * chunk + j) * dkp + d4 * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
+        for (int e = tid; e < cnp * 2 * M; e += blockDim.x) {
+            const int j = e / (2 * M), w = e - j * 2 * M;
+            if (j < cn) dr_cp_async4(gram + e, grp + ((size_t)(start + c0 + j) * H + h) * GW + 4 * dkr + w);
+            else gram[e] = 0.0f;
+        }
+        for (int e = tid; e < cnp * cols; e += blockDim.x) {
+            const int j = e / cols, cc = e - j * cols;
+            const int c = part * cols + cc;
+            if (j < cn && c < dv) dr_cp_async4(v_s + e, prep + (size_t)(start + c0 + j) * P + 2 * G * dk + (size_t)h * dv + c);
+            else v_s[e] = 0.0f;
+        }
+        for (int j = tid; j < cnp; j += blockDim.x) {
+            if (j < cn) dr_cp_async4(b_s + j, prep + (size_t)(start + c0 + j) * P + C + (size_t)H * dk + h);
+            else b_s[j] = 0.0f;
+        }
     };
 
     stage(0, 0);
@@ -184,60 +258,17 @@ __global__ void __launch_bounds__(256) cdelta_recurrence_kernel(
     int b = 0;
     for (int c0 = 0; c0 < n; c0 += chunk, b ^= 1) {
         const int cn = n - c0 < chunk ? n - c0 : chunk;
-        if (c0 + chunk < n) stage(c0 + chunk, b ^ 1);
+        if (c0 + chunk < n) stage(c0 + chunk, b ^ 1);        // the other buffer was read a chunk ago; the barrier below stands between
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
-        float* q_s = sm + b * buf_floats;
-        float* k_s = q_s + chunk * dkp;
-        float* l_s = k_s + chunk * dkp;
-        float* kt_s = l_s + chunk * dkp;
-        const float* v_s = kt_s + chunk * dkp;
+        const float* kt_s = sm + b * buf_floats;
+        const float* q_s = kt_s + chunk * dkp;
+        const float* kf_s = q_s + chunk * dkp;
+        const float* el_s = kf_s + chunk * dkp;
+        const float* v_s = el_s + chunk * dkp;
         const float* b_s = v_s + chunk * cols;
-        float* gram = const_cast<float*>(b_s) + chunk;       // [groups][2][M][M]
-        const int cnp = (cn + M - 1) / M * M;
-        const int groups = cnp / M;
-        // running sums of the log decays inside every group, a (group, channel) a thread
-        for (int e = tid; e < groups * dkp; e += blockDim.x) {
-            const int grp = e / dkp, d = e - grp * dkp;
-            float run = 0.0f;
-#pragma unroll
-            for (int t = 0; t < M; t++) {
-                run += l_s[(grp * M + t) * dkp + d];
-                l_s[(grp * M + t) * dkp + d] = run;
-            }
-        }
-        __syncthreads();
-        for (int e = tid; e < cnp * 2 * M; e += blockDim.x) {        // entry e = ((group * 2 + which) * M + t) * M + j
-            const int jj = e % M, t = (e / M) % M, which = (e / (M * M)) % 2, grp = e / (2 * M * M);
-            float acc = 0.0f;
-            if (which ? jj >= t : jj > t) {
-                const float* x = k_s + (grp * M + t) * dkp;
-                const float* y = (which ? q_s : k_s) + (grp * M + jj) * dkp;
-                const float* lt = l_s + (grp * M + t) * dkp;
-                const float* lj = l_s + (grp * M + jj) * dkp;
-                float a0 = 0.0f, a1 = 0.0f;
-                for (int ii = 0; ii < dkp; ii += 2) {
-                    const int i0 = (ii + 2 * tid) & (dkp - 1);       // neighbouring threads start at other banks
-                    a0 = fmaf(x[i0] * y[i0], jj == t ? 1.0f : expf(lj[i0] - lt[i0]), a0);
-                    a1 = fmaf(x[i0 + 1] * y[i0 + 1], jj == t ? 1.0f : expf(lj[i0 + 1] - lt[i0 + 1]), a1);
-                }
-                acc = a0 + a1;
-            }
-            gram[e] = acc;
-        }
-        __syncthreads();
-        // kt = e^{L_t} k_t,  q <- e^{L_t} q_t,  k <- e^{L_M - L_t} k_t; the last row of a group's l stays: e^{L_M} is taken below
-        for (int e = tid; e < cnp * dkp; e += blockDim.x) {
-            const int j = e / dkp, d = e - j * dkp;
-            const int last = (j / M) * M + M - 1;
-            const float lt = l_s[e], lm = l_s[last * dkp + d];
-            const float et = expf(lt), kv = k_s[e];
-            kt_s[e] = et * kv;
-            q_s[e] *= et;
-            k_s[e] = expf(lm - lt) * kv;
-        }
-        __syncthreads();
+        const float* gram = b_s + chunk;
         const int clc = cl < cols ? cl : 0;
         for (int j0 = 0; j0 < cn; j0 += M) {
             float D[M], E[M];
@@ -264,27 +295,27 @@ __global__ void __launch_bounds__(256) cdelta_recurrence_kernel(
                     E[t] += __shfl_xor_sync(0xffffffffu, E[t], w);
                 }
             }
-            const float* gk = gram + (j0 / M) * 2 * M * M;
-            const float* gq = gk + M * M;
             float uw[M];
 #pragma unroll
             for (int t = 0; t < M; t++) {
+                const float* gk = gram + (j0 + t) * 2 * M;
                 const float u = b_s[j0 + t] * (v_s[(j0 + t) * cols + clc] - D[t]);
 #pragma unroll
-                for (int j = t + 1; j < M; j++) D[j] = fmaf(gk[t * M + j], u, D[j]);
+                for (int j = t + 1; j < M; j++) D[j] = fmaf(gk[j], u, D[j]);
 #pragma unroll
-                for (int j = t; j < M; j++) E[j] = fmaf(gq[t * M + j], u, E[j]);
+                for (int j = t; j < M; j++) E[j] = fmaf(gk[M + j], u, E[j]);
                 if (live && r == 0 && j0 + t < cn) o[((size_t)(start + c0 + j0 + t) * H + h) * dv + col] = E[t];
                 uw[t] = u;
             }
-            const float4* lm = reinterpret_cast<const float4*>(l_s + (j0 + M - 1) * dkp) + r;
+            const int lastj = j0 + M - 1 < cn ? j0 + M - 1 : cn - 1;       // the group's last token holds e^{L} of the whole group
+            const float4* lm = reinterpret_cast<const float4*>(el_s + lastj * dkp) + r;
 #pragma unroll
             for (int i = 0; i < KPT / 4; i++) {
                 const float4 lv = lm[i * R];
-                float x0 = expf(lv.x) * s[4 * i], x1 = expf(lv.y) * s[4 * i + 1], x2 = expf(lv.z) * s[4 * i + 2], x3 = expf(lv.w) * s[4 * i + 3];
+                float x0 = lv.x * s[4 * i], x1 = lv.y * s[4 * i + 1], x2 = lv.z * s[4 * i + 2], x3 = lv.w * s[4 * i + 3];
 #pragma unroll
                 for (int t = 0; t < M; t++) {
-                    const float4 kv = (reinterpret_cast<const float4*>(k_s + (j0 + t) * dkp) + r)[i * R];
+                    const float4 kv = (reinterpret_cast<const float4*>(kf_s + (j0 + t) * dkp) + r)[i * R];
                     x0 = fmaf(kv.x, uw[t], x0); x1 = fmaf(kv.y, uw[t], x1); x2 = fmaf(kv.z, uw[t], x2); x3 = fmaf(kv.w, uw[t], x3);
                 }
                 s[4 * i] = x0; s[4 * i + 1] = x1; s[4 * i + 2] = x2; s[4 * i + 3] = x3;
@@ -360,26 +391,48 @@ VK_API int vk_cdelta_prepare(const float* proj, const float* conv_w, const float
     const int P = cd_prep_width(G, H, dk, dv);
     if (taps > DR_MAX_TAPS) return VK_TOO_LARGE;
     const size_t C = 2 * (size_t)G * dk + (size_t)H * dv;
-    const size_t smem = (C + ra + rg) * sizeof(float);
+    const bool few = tokens <= DR_DEPENDENT_TOKENS;
+    const int tok = few ? 1 : 4;
+    const size_t smem = (C + (size_t)tok * (ra + rg)) * sizeof(float);
     if (smem > 200 * 1024) return VK_TOO_LARGE;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(cdelta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(cdelta_prepare_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(cdelta_prepare_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
     const int wide = (int)((C + 31) / 32 * 32);
-    const int threads = tokens <= DR_DEPENDENT_TOKENS ? (wide < 1024 ? wide : 1024) : 256;
-    if (tokens <= DR_DEPENDENT_TOKENS)
-        return launch_dependent(cdelta_prepare_kernel, dim3(tokens), dim3(threads), smem, stream, proj, conv_w, a_log, dt_bias, a2t, g2t, token_seg,
-                                seg_starts, seg_slots, state, state_stride, (size_t)H * dv * dk, prep, P, G, H, dk, dv, taps, ra, rg);
-    return launch_plain(cdelta_prepare_kernel, dim3(tokens), dim3(threads), smem, stream, proj, conv_w, a_log, dt_bias, a2t, g2t, token_seg,
-                        seg_starts, seg_slots, state, state_stride, (size_t)H * dv * dk, prep, P, G, H, dk, dv, taps, ra, rg);
+    if (few)                                                 // few tokens: a channel a thread, and the launch may begin early
+        return launch_dependent(cdelta_prepare_kernel<1>, dim3(tokens), dim3(wide < 1024 ? wide : 1024), smem, stream, proj, conv_w, a_log, dt_bias,
+                                a2t, g2t, token_seg, seg_starts, seg_slots, state, state_stride, (size_t)H * dv * dk, prep, P, tokens, G, H, dk, dv,
+                                taps, ra, rg);
+    return launch_plain(cdelta_prepare_kernel<4>, dim3((tokens + 3) / 4), dim3(256), smem, stream, proj, conv_w, a_log, dt_bias, a2t, g2t, token_seg,
+                        seg_starts, seg_slots, state, state_stride, (size_t)H * dv * dk, prep, P, tokens, G, H, dk, dv, taps, ra, rg);
 }
 
-VK_API int vk_cdelta_recurrence(const float* prep, const float* proj, int proj_width, const int32_t* seg_starts, const int32_t* seg_slots,
-                                float* state, size_t state_stride, float* o, int segments, int tokens, int G, int H, int dk, int dv, int taps,
-                                cudaStream_t stream) {
-    if (segments <= 0) return VK_OK;
+// Floats of the scratch between the groups kernel and the recurrence for a step of `tokens` tokens.
+VK_API size_t vk_cdelta_group_floats(int tokens, int H, int dk) { return (size_t)tokens * H * (4 * ((dk + 3) / 4 * 4) + 8); }
+
+// Two launches: the groups' vectors and products for all tokens side by side (into grp, vk_cdelta_group_floats), then the
+// recurrence, which also writes the state and the convolution's memory.
+VK_API int vk_cdelta_recurrence(const float* prep, const float* proj, int proj_width, const int32_t* token_seg, const int32_t* seg_starts,
+                                const int32_t* seg_slots, float* state, size_t state_stride, float* grp, float* o, int segments, int tokens,
+                                int G, int H, int dk, int dv, int taps, cudaStream_t stream) {
+    if (segments <= 0 || tokens <= 0) return VK_OK;
     if (G <= 0 || H <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1) return VK_BAD_SHAPE;
-    const int vec = dk % 4 == 0 && (H * dv) % 4 == 0 && ((uintptr_t)prep % 16) == 0 && ((uintptr_t)state % 16) == 0 && state_stride % 4 == 0;
+    if (((uintptr_t)grp % 16) || ((uintptr_t)prep % 4)) return VK_BAD_ALIGNMENT;
+    const int vec = dk % 4 == 0 && ((uintptr_t)state % 16) == 0 && state_stride % 4 == 0;     // the state's rows in 16-byte pieces
     if (taps > DR_MAX_TAPS || dk > 32 * DR_KPT || H > 65535) return VK_TOO_LARGE;
     const int P = cd_prep_width(G, H, dk, dv);
+    const int M = tokens > 1 ? 4 : 1;                        // tokens taken together (see the kernels); no segment is longer than the step
+    const bool dependent = tokens <= DR_DEPENDENT_TOKENS;
+    {
+        const int grid = (tokens * H + 7) / 8;
+        int rc;
+        if (M == 1) rc = dependent ? launch_dependent(cdelta_groups_kernel<1>, dim3(grid), dim3(256), 0, stream, prep, P, token_seg, seg_starts, grp, tokens, G, H, dk, dv)
+                                   : launch_plain(cdelta_groups_kernel<1>, dim3(grid), dim3(256), 0, stream, prep, P, token_seg, seg_starts, grp, tokens, G, H, dk, dv);
+        else rc = dependent ? launch_dependent(cdelta_groups_kernel<4>, dim3(grid), dim3(256), 0, stream, prep, P, token_seg, seg_starts, grp, tokens, G, H, dk, dv)
+                            : launch_plain(cdelta_groups_kernel<4>, dim3(grid), dim3(256), 0, stream, prep, P, token_seg, seg_starts, grp, tokens, G, H, dk, dv);
+        if (rc != 0) return rc;
+    }
     int R = 1;
     while ((dk + R - 1) / R > DR_KPT) R *= 2;
     while (R < 32 && (dk + R - 1) / R > 8) R *= 2;
@@ -391,22 +444,20 @@ VK_API int vk_cdelta_recurrence(const float* prep, const float* proj, int proj_w
     while ((long long)segments * H * ((dv + cols - 1) / cols) < 148 && cols * R > 64 && cols % 2 == 0) cols /= 2;
     const int parts = (dv + cols - 1) / cols;
     const int threads = ((cols * R + 31) / 32) * 32;
-    const int longest = tokens > 0 ? tokens : 1;
-    const int M = longest > 1 ? 4 : 1;
     int chunk = 64;
     auto bytes = [&](int c) { return (size_t)2 * c * (4 * R * kpt + cols + 1 + 2 * M) * sizeof(float); };
-    while (chunk > 8 && (chunk / 2 >= longest || bytes(chunk) > 64 * 1024)) chunk /= 2;
+    while (chunk > 8 && (chunk / 2 >= tokens || bytes(chunk) > 64 * 1024)) chunk /= 2;
     const size_t smem = bytes(chunk);
     if (smem > 200 * 1024) return VK_TOO_LARGE;
 #define GO(K, MM)                                                                                                                        \
     {                                                                                                                                    \
         auto kern = cdelta_recurrence_kernel<K, MM>;                                                                                     \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                       \
-        if (tokens <= DR_DEPENDENT_TOKENS)                                                                                               \
-            return launch_dependent(kern, dim3(segments, H, parts), dim3(threads), smem, stream, prep, P, proj, proj_width, seg_starts,  \
+        if (dependent)                                                                                                                   \
+            return launch_dependent(kern, dim3(segments, H, parts), dim3(threads), smem, stream, prep, P, grp, proj, proj_width, seg_starts, \
                                     seg_slots, state, state_stride, (size_t)H * dv * dk, o, G, H, dk, dv, taps, R, cols, chunk, vec);    \
-        return launch_plain(kern, dim3(segments, H, parts), dim3(threads), smem, stream, prep, P, proj, proj_width, seg_starts, seg_slots, \
-                            state, state_stride, (size_t)H * dv * dk, o, G, H, dk, dv, taps, R, cols, chunk, vec);                      \
+        return launch_plain(kern, dim3(segments, H, parts), dim3(threads), smem, stream, prep, P, grp, proj, proj_width, seg_starts,     \
+                            seg_slots, state, state_stride, (size_t)H * dv * dk, o, G, H, dk, dv, taps, R, cols, chunk, vec);            \
     }
     if (M == 1) {
         if (kpt == 4) GO(4, 1) else if (kpt == 8) GO(8, 1) else if (kpt == 16) GO(16, 1) else GO(32, 1)

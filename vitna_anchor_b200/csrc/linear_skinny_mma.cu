@@ -46,7 +46,7 @@ struct MmaParams {
     const int32_t* slot;
     __nv_bfloat16* cache;
     int nh, nkv, hd, page_size;
-    int act;                     // ME_SAME: an activation on the float32 sums before they are rounded (activate_rt; 0 none)
+    int act;                     // ME_SAME: an activation on the float32 sums before they are rounded (activate_rt; 0 none); ME_SWIGLU: the gate's function (0: silu)
 };
 
 __device__ __forceinline__ void mm_cp_async16(void* dst, const void* src) {
@@ -91,7 +91,7 @@ __device__ __forceinline__ void mma_finish(const MmaParams& p, int u, int r0, in
         if (has1) o[r1] = (pre ? old[1] : o[r1]) + a1;
     } else if (EPI == ME_SWIGLU) {
         const float g = bf16_round(a0), up = bf16_round(a1);
-        reinterpret_cast<T*>(p.out)[(size_t)m * (p.N / 2) + u] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
+        reinterpret_cast<T*>(p.out)[(size_t)m * (p.N / 2) + u] = __float2bfloat16_rn((p.act ? activate_rt(p.act, g) : g / (1.0f + expf(-g))) * up);
     } else {
         const int half = p.hd / 2, rot_units = (p.nh + p.nkv) * half;
         const int s = pre ? pre_slot : p.slot[m];
@@ -878,7 +878,7 @@ static int linear_skinny_mma_impl(const void* x, const int32_t* rows, const floa
                                   const float* sin_t, const int32_t* slot, void* cache, int nh, int nkv, int hd, int page_size, int act,
                                   cudaStream_t stream) {
     if (M <= 0 || N <= 0) return VK_OK;
-    if (K <= 0 || ldx < K || epi < 0 || epi > 4 || K % 32 != 0 || act < 0 || act > 3 || (act && epi != ME_SAME)) return VK_BAD_SHAPE;
+    if (K <= 0 || ldx < K || epi < 0 || epi > 4 || K % 32 != 0 || act < 0 || act > 3 || (act && epi != ME_SAME && epi != ME_SWIGLU)) return VK_BAD_SHAPE;
     if (M > 64) return VK_TOO_LARGE;
     if (((uintptr_t)w % 16) || ((uintptr_t)x % 16)) return VK_BAD_ALIGNMENT;
     if (norm_w ? (ldx % 4 != 0 || ((uintptr_t)norm_w % 16)) : (ldx % 8 != 0)) return VK_BAD_ALIGNMENT;
@@ -905,5 +905,14 @@ VK_API int vk_linear_skinny_mma(const void* x, const int32_t* rows, const float*
 VK_API int vk_linear_skinny_mma_act(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
                                     int M, int N, int K, int ldx, int act, cudaStream_t stream) {
     return linear_skinny_mma_impl(x, rows, norm_w, eps, w, out, M, N, K, ldx, ME_SAME, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0,
+                                  act, stream);
+}
+
+// out (bfloat16) [M, N/2] = act(x' @ gate.T) * (x' @ up.T) for at most 64 rows; w [N, K]: gate rows, then up rows; act as activate_rt
+// numbers them (the gate's function on the rounded sums, in the epilogue).
+VK_API int vk_linear_skinny_mma_gated(const void* x, const int32_t* rows, const float* norm_w, float eps, const void* w, void* out,
+                                      int M, int N, int K, int ldx, int act, cudaStream_t stream) {
+    if (act < 1) return VK_BAD_SHAPE;
+    return linear_skinny_mma_impl(x, rows, norm_w, eps, w, out, M, N, K, ldx, ME_SWIGLU, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0,
                                   act, stream);
 }

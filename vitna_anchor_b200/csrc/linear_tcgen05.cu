@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(TC_THREADS) linear_tcgen05_kernel(const __grid
                         for (int e = 0; e < 2; e++) {
                             const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[j + e])));
                             const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[j + e])));
-                            a[e] = tc_silu_mul(gte, up);
+                            a[e] = ex.act ? activate_rt(ex.act, gte) * up : tc_silu_mul(gte, up);
                         }
                         __nv_bfloat162 v = __floats2bfloat162_rn(a[0], a[1]);
                         packed[j / 2] = *reinterpret_cast<uint32_t*>(&v);
@@ -522,7 +522,7 @@ __global__ void __launch_bounds__(TW_THREADS, 1) linear_tcgen05_wide_kernel(cons
                                 for (int e = 0; e < 2; e++) {
                                     const float gte = __bfloat162float(__float2bfloat16_rn(__uint_as_float(gr[q + e])));
                                     const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ur[q + e])));
-                                    v[e] = tc_silu_mul(gte, up);
+                                    v[e] = ex.act ? activate_rt(ex.act, gte) * up : tc_silu_mul(gte, up);
                                 }
                                 __nv_bfloat162 pk = __floats2bfloat162_rn(v[0], v[1]);
                                 packed[q / 2] = *reinterpret_cast<uint32_t*>(&pk);
@@ -800,8 +800,23 @@ VK_API int vk_linear_tcgen05_act(const void* x, const void* w, void* out, int M,
 
 // x [M, K] bfloat16 (row stride ldx), w [2*inter, K] bfloat16 with gate rows then up rows, out [M, inter] bfloat16 =
 // silu(x gate^T) * (x up^T).  inter a multiple of 8.
+static int linear_tcgen05_gated_impl(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int act, int* error,
+                                     cudaStream_t stream);
+
 VK_API int vk_linear_tcgen05_swiglu(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int* error,
                                     cudaStream_t stream) {
+    return linear_tcgen05_gated_impl(x, w, out, M, inter, K, ldx, 0, error, stream);
+}
+
+// The same with another function of the gate: act as activate_rt numbers them (1 gelu erf, 2 gelu tanh, 3 silu by expf).
+VK_API int vk_linear_tcgen05_gated(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int act, int* error,
+                                   cudaStream_t stream) {
+    if (act < 1 || act > 3) return VK_BAD_SHAPE;
+    return linear_tcgen05_gated_impl(x, w, out, M, inter, K, ldx, act, error, stream);
+}
+
+static int linear_tcgen05_gated_impl(const void* x, const void* w, void* out, int M, int inter, int K, int ldx, int act, int* error,
+                                     cudaStream_t stream) {
     if (M <= 0 || inter <= 0) return VK_OK;
     if (K <= 0 || ldx < K || !error || K % 8 != 0 || ldx % 8 != 0 || inter % 8 != 0) return VK_BAD_SHAPE;
     if (((uintptr_t)x % 16) || ((uintptr_t)w % 16) || ((uintptr_t)out % 16)) return VK_BAD_ALIGNMENT;
@@ -809,6 +824,7 @@ VK_API int vk_linear_tcgen05_swiglu(const void* x, const void* w, void* out, int
     CUtensorMap mx, mw;
     TcExtra ex{};
     ex.inter = inter;
+    ex.act = act;
     if (wide_takes(M, inter, K, TW_BN / 2)) {
         // Tiles of 128 x 96 output columns (192 weight rows) where they come out sooner than tiles of 128 x 128: a block
         // walks through ceil(tiles / blocks) tiles, and at the 135M and 360M sizes the last round of the wider tile is

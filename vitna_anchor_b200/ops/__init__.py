@@ -1094,18 +1094,24 @@ def channel_delta_prep_width(G: int, H: int, dk: int, dv: int) -> int:
     return (2 * G * dk + 2 * H * dv + H * dk + H + 3) // 4 * 4
 
 
+def channel_delta_group_floats(tokens: int, H: int, dk: int) -> int:
+    """Floats of the scratch that holds, for every token and head, what its group of tokens needs besides the state."""
+    return tokens * H * (4 * ((dk + 3) // 4 * 4) + 8)
+
+
 def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, a2t: torch.Tensor,
                        g2t: torch.Tensor, norm_w: torch.Tensor, eps: float, token_seg: torch.Tensor, seg_starts: torch.Tensor,
-                       seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor, o: torch.Tensor, out: torch.Tensor, G: int, H: int,
-                       dk: int, dv: int, taps: int) -> torch.Tensor:
+                       seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor, groups: torch.Tensor, o: torch.Tensor, out: torch.Tensor,
+                       G: int, H: int, dk: int, dv: int, taps: int) -> torch.Tensor:
     """The delta rule whose decay differs by head and key channel, from the projections to the input of the output projection.
     proj float32 [T, 2 G dk + H dv + H + ra + rg] = q | k | v | b | a1 | g1;  a2t float32 [ra, H dk] and g2t [rg, H dv], the wide
     halves of the two low-rank projections, transposed;  dt_bias [H dk];  a_log [H];  norm_w [dv];  state float32
-    [slots, delta_state_floats];  prep [T, channel_delta_prep_width] and o [T, H dv] float32 scratch;  out [T, H dv] in the compute
-    dtype.  Three launches: prepare, recurrence (which also writes the state), gate."""
+    [slots, delta_state_floats];  prep [T, channel_delta_prep_width], groups (flat, channel_delta_group_floats(T, H, dk)) and o [T, H dv]
+    float32 scratch;  out [T, H dv] in the compute dtype.  Four launches: prepare, what the groups of tokens need besides the state
+    (all groups side by side), the recurrence (which also writes the state), gate."""
     C = 2 * G * dk + H * dv
     for name, t, d in (("proj", proj, 2), ("conv_w", conv_w, 2), ("a_log", a_log, 1), ("dt_bias", dt_bias, 1), ("a2t", a2t, 2), ("g2t", g2t, 2),
-                       ("norm_w", norm_w, 1), ("state", state, 2), ("prep", prep, 2), ("o", o, 2)):
+                       ("norm_w", norm_w, 1), ("state", state, 2), ("prep", prep, 2), ("o", o, 2), ("groups", groups, 1)):
         _req(t, name, torch.float32, d)
     _req(out, "out", dims=2)
     _req(token_seg, "token_seg", torch.int32, 1); _req(seg_starts, "seg_starts", torch.int32, 1); _req(seg_slots, "seg_slots", torch.int32, 1)
@@ -1114,17 +1120,40 @@ def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Te
     if (proj.shape[1] != C + H + ra + rg or conv_w.shape != (C, taps) or a_log.shape[0] != H or dt_bias.shape[0] != H * dk
             or a2t.shape[1] != H * dk or g2t.shape[1] != H * dv or norm_w.shape[0] != dv
             or prep.shape != (T, channel_delta_prep_width(G, H, dk, dv)) or o.shape != (T, H * dv) or out.shape != (T, H * dv)
-            or state.shape[1] != delta_state_floats(G, H, dk, dv, taps) or token_seg.shape[0] != T or seg_starts.shape[0] != S + 1):
+            or state.shape[1] != delta_state_floats(G, H, dk, dv, taps) or token_seg.shape[0] != T or seg_starts.shape[0] != S + 1
+            or groups.numel() < channel_delta_group_floats(T, H, dk)):
         raise KernelError("channel_delta_rule: shapes do not fit the head counts")
     stride = ctypes.c_size_t(state.stride(0))
     _check(lib().vk_cdelta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(a2t), _p(g2t), _p(token_seg), _p(seg_starts), _p(seg_slots),
                                    _p(state), stride, _p(prep), T, G, H, dk, dv, taps, ra, rg, _stream()), "cdelta_prepare")
-    _check(lib().vk_cdelta_recurrence(_p(prep), _p(proj), proj.shape[1], _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o), S, T, G, H, dk,
-                                      dv, taps, _stream()), "cdelta_recurrence")
+    _check(lib().vk_cdelta_recurrence(_p(prep), _p(proj), proj.shape[1], _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
+                                      _p(groups), _p(o), S, T, G, H, dk, dv, taps, _stream()), "cdelta_recurrence")
+    global _launches
+    _launches += 1                                  # two kernels
     _check(lib().vk_cdelta_gate(_p(o), _p(prep), _p(norm_w), ctypes.c_float(eps), _p(out), T, G, H, dk, dv, _dt(out), _stream()), "cdelta_gate")
     return out
 
 
 def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, gu: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
-    """out = act(x @ w_gate.T) * (x @ w_up.T) for the two matrices stacked by rows; gu [T, 2I] is scratch in x's dtype."""
+    """out = act(x @ w_gate.T) * (x @ w_up.T) for the two matrices stacked by rows; kind one of ACTIVATIONS.  In bfloat16 the gate's
+    function and the product with the other half are the epilogue of the few-rows tensor-core product (up to 64 rows) or of the
+    tcgen05 product; elsewhere (float32, sizes those refuse) the product writes gu [T, 2I] (scratch in x's dtype) and a launch of its
+    own follows."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"linear_gated: {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    M, K = x.shape
+    inter = w_gate_up.shape[0] // 2
+    if (x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.shape == (2 * inter, K) and tuple(out.shape) == (M, inter)
+            and out.dtype == x.dtype and out.is_contiguous() and w_gate_up.is_contiguous()):
+        act = ACTIVATIONS[kind] + 1
+        if (skinny_takes(x.dtype, M, K, 2 * inter) and K % 32 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+                and w_gate_up.data_ptr() % 16 == 0):
+            ldx = x.stride(0) if M > 1 else max(K, x.stride(0))
+            _check(lib().vk_linear_skinny_mma_gated(_p(x), _p(None), _p(None), ctypes.c_float(0.0), _p(w_gate_up), _p(out), M, 2 * inter, K, ldx,
+                                                    act, _stream()), "linear_skinny_mma_gated")
+            return out
+        if M > SKINNY_MAX_ROWS and inter % 8 == 0 and tcgen05_takes(x, w_gate_up) and out.data_ptr() % 16 == 0:
+            _check(lib().vk_linear_tcgen05_gated(_p(x), _p(w_gate_up), _p(out), M, inter, K, x.stride(0), act, _p(error_word()), _stream()),
+                   "linear_tcgen05_gated")
+            return out
     return act_mul(linear(x, w_gate_up, gu, LINEAR_SAME), out, kind)

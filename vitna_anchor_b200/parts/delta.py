@@ -119,6 +119,8 @@ class ChannelDeltaRule(Mixer):
         out = ops.channel_delta_rule(proj, self.conv, self.a_log, self.dt_bias, self.a2t, self.g2t, self.norm_weight, self.eps, ctx.token_seg,
                                      ctx.seg_starts, ctx.seg_slots, cache.state,
                                      ws.rows("cdelta.prep", T, ops.channel_delta_prep_width(self.G, self.H, self.dk, self.dv), torch.float32),
+                                     ws.flat(f"cdelta.groups/{self.H}/{self.dk}", ops.channel_delta_group_floats(ws.max_tokens, self.H, self.dk),
+                                             torch.float32),
                                      ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
                                      self.G, self.H, self.dk, self.dv, self.taps)
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
