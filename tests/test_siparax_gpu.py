@@ -392,6 +392,37 @@ def test_the_channel_delta_kernels_against_the_recurrence_written_out():
             assert np.abs(np.concatenate(outs[i]) - want).max() < 2e-5 * max(1.0, np.abs(want).max()), (G, H, dk, dv, taps, i)
 
 
+def test_the_one_kernel_channel_delta_rule_for_single_tokens_gives_what_the_other_kernels_give():
+    from vitna_anchor_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(4)
+    r = lambda *s: torch.randn(*s, generator=g, device="cuda")
+    for (G, H, dk, dv, taps, ra, rg) in ((1, 2, 16, 8, 3, 3, 5), (3, 9, 64, 64, 4, 16, 16), (4, 16, 128, 128, 4, 8, 24), (1, 3, 40, 7, 1, 2, 2),
+                                         (2, 2, 256, 32, 2, 4, 4), (1, 1, 8, 300, 2, 5, 1)):
+        assert ops.channel_delta_decode_takes(G, H, dk, dv, taps, ra, rg)
+        C, S = 2 * G * dk + H * dv, 5
+        N = C + H + ra + rg
+        conv, a_log, dt, nw = r(C, taps) * 0.6, r(H) - 1, r(H * dk) * 2, 1 + 0.1 * r(dv)
+        a2t, g2t = r(ra, H * dk) * 2, r(rg, H * dv)
+        slots = torch.tensor([3, -1, 0, 6, 2], dtype=torch.int32, device="cuda")         # one padding segment
+        seg_starts = torch.arange(S + 1, dtype=torch.int32, device="cuda")
+        token_seg = torch.arange(S, dtype=torch.int32, device="cuda")
+        states = [r(8, ops.delta_state_floats(G, H, dk, dv, taps)) * 0.3 for _ in range(2)]
+        states[1].copy_(states[0])
+        for step in range(3):                                # the state and the convolution's memory are carried
+            proj = r(S, N)
+            outs = []
+            for single in (False, True):
+                out = torch.zeros(S, H * dv, device="cuda")
+                ops.channel_delta_rule(proj, conv, a_log, dt, a2t, g2t, nw, 1e-5, token_seg, seg_starts, slots, states[single],
+                                       torch.empty(S, ops.channel_delta_prep_width(G, H, dk, dv), device="cuda"),
+                                       torch.empty(ops.channel_delta_group_floats(S, H, dk), device="cuda"), torch.zeros(S, H * dv, device="cuda"),
+                                       out, G, H, dk, dv, taps, single_tokens=single)
+                outs.append(out)
+            live = slots >= 0
+            assert torch.allclose(outs[0][live], outs[1][live], rtol=1e-4, atol=1e-5), (G, H, dk, dv, taps, step)
+            assert torch.allclose(states[0], states[1], rtol=1e-4, atol=1e-5)
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # the engine's own entry point and scheduler, the command line, the replay program
 # ---------------------------------------------------------------------------------------------------------------

@@ -375,6 +375,146 @@ __global__ void __launch_bounds__(256) cdelta_gate_kernel(const float* __restric
     for (int d = lane; d < dv; d += 32) out[(size_t)unit * dv + d] = from_f32<T>(((in[d] * inv) * norm_w[d]) * gate[d]);
 }
 
+// Single decoded tokens: everything between the projections and the output projection in ONE kernel.  grid (segments, G): a
+// block has a key head's q and k and the H/G value heads that read them, so every channel of the convolution belongs to one
+// block, which reads its memory, uses it and moves it on.  The block works out its heads' decays (dk values a head) and gates
+// from the narrow halves a1 and g1, then takes the state's columns (H/G * dv of them) in passes of blockDim / R columns, R lanes a
+// column, KPT <= 16 values a lane in pieces of four.
+template <typename T, int KPT>
+__global__ void __launch_bounds__(1024) cdelta_decode_kernel(
+    const float* __restrict__ proj, const float* __restrict__ conv_w, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+    const float* __restrict__ a2t, const float* __restrict__ g2t, const float* __restrict__ norm_w, float eps,
+    const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots, float* __restrict__ state, size_t state_stride,
+    size_t conv_off, T* __restrict__ out, int G, int H, int dk, int dv, int taps, int ra, int rg, int R) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float scal[2];
+    const int seg = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    dependency_wait();
+    let_dependents_start();
+    const int slot = seg_slots[seg];
+    if (slot < 0) return;                                    // a padding segment of a captured batch
+    const int t = seg_starts[seg];
+    const int HG = H / G, C = 2 * G * dk + H * dv, N = C + H + ra + rg;
+    const int dkp = R * KPT, cols = HG * dv;
+    float* row = state + (size_t)slot * state_stride;
+    float* cs = row + conv_off;                              // [taps-1][C]
+    float* q_s = sm;                                         // [dkp]
+    float* k_s = q_s + dkp;                                  // [dkp]
+    float* d_s = k_s + dkp;                                  // [HG][dkp] the decays (16-byte aligned like q_s and k_s)
+    float* v_s = d_s + HG * dkp;                             // [cols]
+    float* o_s = v_s + cols;                                 // [cols]
+    float* g_s = o_s + cols;                                 // [cols] the output gate
+    float* lr = g_s + cols;                                  // a1 | g1
+    const float* in = proj + (size_t)t * N;
+
+    for (int idx = tid; idx < 2 * dkp + cols; idx += blockDim.x) {
+        int ch = -1;
+        if (idx < dkp) { if (idx < dk) ch = g * dk + idx; }
+        else if (idx < 2 * dkp) { if (idx - dkp < dk) ch = (G + g) * dk + (idx - dkp); }
+        else ch = 2 * G * dk + g * cols + (idx - 2 * dkp);
+        float val = 0.0f;
+        if (ch >= 0) {
+            float x[DR_MAX_TAPS], w[DR_MAX_TAPS];
+#pragma unroll
+            for (int j = 0; j < DR_MAX_TAPS; j++)
+                if (j < taps) {
+                    x[j] = j == 0 ? in[ch] : cs[(size_t)(taps - 1 - j) * C + ch];
+                    w[j] = conv_w[(size_t)ch * taps + (taps - 1 - j)];
+                }
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = DR_MAX_TAPS - 1; j >= 0; j--)
+                if (j < taps) acc = fmaf(w[j], x[j], acc);
+            val = silu_f(acc);
+#pragma unroll
+            for (int rr = 0; rr < DR_MAX_TAPS; rr++)          // row rr becomes the input of taps-2-rr tokens ago
+                if (rr < taps - 1) cs[(size_t)rr * C + ch] = x[taps - 2 - rr];
+        }
+        if (idx < 2 * dkp) sm[idx] = val;                    // q_s, then k_s
+        else v_s[idx - 2 * dkp] = val;
+    }
+    for (int r = tid; r < ra + rg; r += blockDim.x) lr[r] = in[C + H + r];
+    __syncthreads();
+    if (warp < 2) {                                          // unit length for q (and dk^-1/2) and k
+        const float* v = warp == 0 ? q_s : k_s;
+        float ss = 0.0f;
+        for (int d = lane; d < dk; d += 32) ss = fmaf(v[d], v[d], ss);
+        ss = warp_sum(ss);
+        float inv = 1.0f / sqrtf(ss + 1e-6f);
+        if (warp == 0) inv *= 1.0f / sqrtf((float)dk);
+        if (lane == 0) scal[warp] = inv;
+    }
+    const int HK = H * dk, HV = H * dv;
+    for (int e = tid; e < HG * dkp; e += blockDim.x) {       // this block's heads' decays (1 where the lanes hold nothing)
+        const int hh = e / dkp, d = e - hh * dkp;
+        float dec = 1.0f;
+        if (d < dk) {
+            const int c = (g * HG + hh) * dk + d;
+            float acc = 0.0f;
+            for (int r = 0; r < ra; r++) acc = fmaf(a2t[(size_t)r * HK + c], lr[r], acc);
+            dec = expf(-expf(a_log[g * HG + hh]) * softplus_f(acc + dt_bias[c]));
+        }
+        d_s[e] = dec;
+    }
+    for (int e = tid; e < cols; e += blockDim.x) {
+        const int c = g * cols + e;
+        float acc = 0.0f;
+        for (int r = 0; r < rg; r++) acc = fmaf(g2t[(size_t)r * HV + c], lr[ra + r], acc);
+        g_s[e] = sigmoid_f(acc);
+    }
+    __syncthreads();
+    for (int d = tid; d < dk; d += blockDim.x) { q_s[d] *= scal[0]; k_s[d] *= scal[1]; }
+    __syncthreads();
+
+    const int r = tid % R, per_pass = blockDim.x / R;
+    for (int c0 = 0; c0 < cols; c0 += per_pass) {
+        const int ci = c0 + tid / R;
+        const bool live = ci < cols;
+        const int hh = live ? ci / dv : 0, col = live ? ci % dv : 0, h = g * HG + hh;
+        const float beta = sigmoid_f(in[C + h]);
+        float* srow = row + ((size_t)h * dv + col) * dk;
+        const float* dec = d_s + hh * dkp;
+        float s[KPT];
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < KPT / 4; i++) {
+            const int k0 = (i * R + r) * 4;
+            const float4 v = (live && k0 < dk) ? *reinterpret_cast<const float4*>(srow + k0) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4 kv = *reinterpret_cast<const float4*>(k_s + k0), dv4 = *reinterpret_cast<const float4*>(dec + k0);
+            s[4 * i] = dv4.x * v.x; s[4 * i + 1] = dv4.y * v.y; s[4 * i + 2] = dv4.z * v.z; s[4 * i + 3] = dv4.w * v.w;
+            a0 = fmaf(s[4 * i], kv.x, fmaf(s[4 * i + 2], kv.z, a0));
+            a1 = fmaf(s[4 * i + 1], kv.y, fmaf(s[4 * i + 3], kv.w, a1));
+        }
+        float dot = a0 + a1;
+        for (int w = R >> 1; w > 0; w >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+        const float u = beta * (v_s[live ? ci : 0] - dot);
+        a0 = a1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < KPT / 4; i++) {
+            const int k0 = (i * R + r) * 4;
+            const float4 kv = *reinterpret_cast<const float4*>(k_s + k0), qv = *reinterpret_cast<const float4*>(q_s + k0);
+            const float x0 = fmaf(kv.x, u, s[4 * i]), x1 = fmaf(kv.y, u, s[4 * i + 1]);
+            const float x2 = fmaf(kv.z, u, s[4 * i + 2]), x3 = fmaf(kv.w, u, s[4 * i + 3]);
+            a0 = fmaf(x0, qv.x, fmaf(x2, qv.z, a0));
+            a1 = fmaf(x1, qv.y, fmaf(x3, qv.w, a1));
+            if (live && k0 < dk) *reinterpret_cast<float4*>(srow + k0) = make_float4(x0, x1, x2, x3);
+        }
+        float acc = a0 + a1;
+        for (int w = R >> 1; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+        if (live && r == 0) o_s[ci] = acc;
+    }
+    __syncthreads();
+    for (int hh = warp; hh < HG; hh += (int)(blockDim.x >> 5)) {                  // o / rms(o) * w * gate, a warp a head
+        const int h = g * HG + hh;
+        const float* ov = o_s + hh * dv;
+        float ss = 0.0f;
+        for (int d = lane; d < dv; d += 32) ss = fmaf(ov[d], ov[d], ss);
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+        for (int d = lane; d < dv; d += 32) out[((size_t)t * H + h) * dv + d] = from_f32<T>(((ov[d] * inv) * norm_w[d]) * g_s[hh * dv + d]);
+    }
+}
+
 }  // namespace vk
 
 using namespace vk;
@@ -480,4 +620,47 @@ VK_API int vk_cdelta_gate(const float* o, const float* prep, const float* norm_w
     }
     if (dtype == 0) return launch_plain(cdelta_gate_kernel<float>, dim3(grid), dim3(256), 0, stream, o, prep, P, off, norm_w, eps, (float*)out, tokens, H, dv);
     return launch_plain(cdelta_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, o, prep, P, off, norm_w, eps, (__nv_bfloat16*)out, tokens, H, dv);
+}
+
+static size_t cdelta_decode_smem(int G, int H, int dk, int dv, int ra, int rg) {
+    const size_t HG = H / G;
+    return (2 * 32 * 16 + 3 * HG * dv + HG * 32 * 16 + ra + rg) * sizeof(float);       // the most the kernel can ask for
+}
+
+// Whether the one-kernel form for single decoded tokens takes these sizes (key size a multiple of four up to 512).
+VK_API int vk_cdelta_decode_takes(int G, int H, int dk, int dv, int taps, int ra, int rg) {
+    return G > 0 && H > 0 && H % G == 0 && dk % 4 == 0 && dk >= 4 && dk <= 32 * 16 && dv > 0 && taps >= 1 && taps <= DR_MAX_TAPS && ra > 0 &&
+           rg > 0 && cdelta_decode_smem(G, H, dk, dv, ra, rg) <= 160 * 1024;
+}
+
+// Every segment is ONE token.  proj, a2t, g2t as for vk_cdelta_prepare; out [tokens][H*dv] in dtype; the state is read and written.
+VK_API int vk_cdelta_decode(const float* proj, const float* conv_w, const float* a_log, const float* dt_bias, const float* a2t, const float* g2t,
+                            const float* norm_w, float eps, const int32_t* seg_starts, const int32_t* seg_slots, float* state,
+                            size_t state_stride, void* out, int segments, int G, int H, int dk, int dv, int taps, int ra, int rg, int dtype,
+                            cudaStream_t stream) {
+    if (segments <= 0) return VK_OK;
+    if (!vk_cdelta_decode_takes(G, H, dk, dv, taps, ra, rg)) return VK_BAD_SHAPE;
+    if (((uintptr_t)state % 16) || state_stride % 4 || G > 65535) return VK_BAD_ALIGNMENT;
+    const int HG = H / G, cols = HG * dv;
+    int R = 1;
+    while ((dk + R - 1) / R > 16) R *= 2;                    // a lane holds at most sixteen values of a column
+    while (R < 32 && cols * R * 2 <= 256 && (dk + R - 1) / R > 4) R *= 2;      // few columns: more lanes a column
+    int kpt = 4;
+    while (kpt * R < dk) kpt *= 2;
+    const int want = (cols * R + 31) / 32 * 32;
+    const int threads = want < 256 ? 256 : (want > 1024 ? 1024 : want);
+    const size_t smem = (size_t)(2 * R * kpt + 3 * cols + HG * R * kpt + ra + rg) * sizeof(float);
+#define GO(TT, K)                                                                                                                       \
+    {                                                                                                                                   \
+        auto kern = cdelta_decode_kernel<TT, K>;                                                                                        \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+        return launch_dependent(kern, dim3(segments, G), dim3(threads), smem, stream, proj, conv_w, a_log, dt_bias, a2t, g2t, norm_w, eps, \
+                                seg_starts, seg_slots, state, state_stride, (size_t)H * dv * dk, (TT*)out, G, H, dk, dv, taps, ra, rg, R); \
+    }
+    if (dtype == 0) {
+        if (kpt == 4) GO(float, 4) else if (kpt == 8) GO(float, 8) else GO(float, 16)
+    } else {
+        if (kpt == 4) GO(__nv_bfloat16, 4) else if (kpt == 8) GO(__nv_bfloat16, 8) else GO(__nv_bfloat16, 16)
+    }
+#undef GO
 }

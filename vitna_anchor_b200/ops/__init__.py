@@ -1099,16 +1099,22 @@ def channel_delta_group_floats(tokens: int, H: int, dk: int) -> int:
     return tokens * H * (4 * ((dk + 3) // 4 * 4) + 8)
 
 
+def channel_delta_decode_takes(G: int, H: int, dk: int, dv: int, taps: int, ra: int, rg: int) -> bool:
+    """Whether the one-kernel form for single decoded tokens takes these sizes (key size a multiple of 4 up to 512)."""
+    return bool(lib().vk_cdelta_decode_takes(G, H, dk, dv, taps, ra, rg))
+
+
 def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, a2t: torch.Tensor,
                        g2t: torch.Tensor, norm_w: torch.Tensor, eps: float, token_seg: torch.Tensor, seg_starts: torch.Tensor,
                        seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor, groups: torch.Tensor, o: torch.Tensor, out: torch.Tensor,
-                       G: int, H: int, dk: int, dv: int, taps: int) -> torch.Tensor:
+                       G: int, H: int, dk: int, dv: int, taps: int, single_tokens: bool = False) -> torch.Tensor:
     """The delta rule whose decay differs by head and key channel, from the projections to the input of the output projection.
     proj float32 [T, 2 G dk + H dv + H + ra + rg] = q | k | v | b | a1 | g1;  a2t float32 [ra, H dk] and g2t [rg, H dv], the wide
     halves of the two low-rank projections, transposed;  dt_bias [H dk];  a_log [H];  norm_w [dv];  state float32
     [slots, delta_state_floats];  prep [T, channel_delta_prep_width], groups (flat, channel_delta_group_floats(T, H, dk)) and o [T, H dv]
     float32 scratch;  out [T, H dv] in the compute dtype.  Four launches: prepare, what the groups of tokens need besides the state
-    (all groups side by side), the recurrence (which also writes the state), gate."""
+    (all groups side by side), the recurrence (which also writes the state), gate.  With single_tokens (every segment is one
+    token; sizes that channel_delta_decode_takes) everything is ONE launch."""
     C = 2 * G * dk + H * dv
     for name, t, d in (("proj", proj, 2), ("conv_w", conv_w, 2), ("a_log", a_log, 1), ("dt_bias", dt_bias, 1), ("a2t", a2t, 2), ("g2t", g2t, 2),
                        ("norm_w", norm_w, 1), ("state", state, 2), ("prep", prep, 2), ("o", o, 2), ("groups", groups, 1)):
@@ -1124,6 +1130,11 @@ def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Te
             or groups.numel() < channel_delta_group_floats(T, H, dk)):
         raise KernelError("channel_delta_rule: shapes do not fit the head counts")
     stride = ctypes.c_size_t(state.stride(0))
+    if single_tokens and T == S and channel_delta_decode_takes(G, H, dk, dv, taps, ra, rg):
+        _check(lib().vk_cdelta_decode(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(a2t), _p(g2t), _p(norm_w), ctypes.c_float(eps),
+                                      _p(seg_starts), _p(seg_slots), _p(state), stride, _p(out), S, G, H, dk, dv, taps, ra, rg, _dt(out),
+                                      _stream()), "cdelta_decode")
+        return out
     _check(lib().vk_cdelta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(a2t), _p(g2t), _p(token_seg), _p(seg_starts), _p(seg_slots),
                                    _p(state), stride, _p(prep), T, G, H, dk, dv, taps, ra, rg, _stream()), "cdelta_prepare")
     _check(lib().vk_cdelta_recurrence(_p(prep), _p(proj), proj.shape[1], _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,

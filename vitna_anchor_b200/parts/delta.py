@@ -80,7 +80,8 @@ class ChannelDeltaRule(Mixer):
         out     = W_o (o / rms(o) * w_norm * sigmoid(W_g2 (W_g1 xn)))
 
     ONE product makes q | k | v | b | W_a1 xn | W_g1 xn with float32 results; the wide halves W_a2 and W_g2 are applied in float32
-    inside the kernel that prepares the recurrence.  The state and its slot are GatedDeltaRule's."""
+    inside the kernel that prepares the recurrence.  The state and its slot are GatedDeltaRule's.  Single decoded tokens take ONE
+    kernel for all of it in the serving routings (the exact 32-bit routing keeps one set of kernels for every step)."""
 
     def __init__(self, hidden: int, num_heads: int, num_key_heads: int, key_dim: int, value_dim: int, taps: int, w_in: torch.Tensor,
                  conv: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, w_a2: torch.Tensor, w_g2: torch.Tensor,
@@ -122,5 +123,6 @@ class ChannelDeltaRule(Mixer):
                                      ws.flat(f"cdelta.groups/{self.H}/{self.dk}", ops.channel_delta_group_floats(ws.max_tokens, self.H, self.dk),
                                              torch.float32),
                                      ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
-                                     self.G, self.H, self.dk, self.dv, self.taps)
+                                     self.G, self.H, self.dk, self.dv, self.taps,
+                                     single_tokens=ctx.decode_only and not (ctx.dtype == torch.float32 and ops.float32_exact()))
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
