@@ -613,7 +613,7 @@ def siparax_work(sz, T):
         "product": (products, 0.0),
         "attention": (n_att * float(T) * (T + 1) * H * (hd + vd), 0.0),
         "delta": (n_delta * T * (6.0 * H * dk * dv + 2.0 * r * H * (dk + dv)), n_delta * T * 4.0 * (delta_rows + 2 * prep + 2 * H * dv)),
-        "between": (0.0, (2 * L + 2) * T * W * 6.0 + L * T * sz["ff"] * 6.0 + n_att * T * (4.0 * (sz["q_rank"] + hd) + 6.0 * H * hd)),
+        "between": (0.0, (2 * L + 2) * T * W * 6.0 + n_att * T * (4.0 * (sz["q_rank"] + hd) + 2.0 * sz["q_rank"] + 4.0 * hd + 4.0 * H * hd + 4.0 * H * vd)),
     }
 
 
