@@ -337,17 +337,20 @@ def test_latent_prepare_and_the_query_rotation(interleaved):
     assert np.abs(gated - q[:, :H * r].reshape(T, H, r) * PS.sigmoid(proj[:, qr + r + rd:])[:, :, None]).max() < 1e-5
 
 
-def test_the_channel_delta_kernels_against_the_recurrence_written_out():
+@pytest.mark.parametrize("chunked", [False, True])
+def test_the_channel_delta_kernels_against_the_recurrence_written_out(chunked):
     """Segments of unequal length on scattered slots, a second step that continues from the state of the first, a padding segment;
     key sizes from 10 to 256, sizes that are no multiples of four, and decays that differ widely between the channels of a head."""
     from vitna_anchor_b200 import ops
     rng = np.random.default_rng(5)
     sizes = ((1, 2, 16, 8, 3, 3, 5), (2, 2, 64, 128, 4, 8, 8), (1, 3, 40, 24, 1, 2, 9), (2, 4, 128, 64, 2, 16, 4), (1, 2, 10, 12, 2, 4, 4),
-             (1, 1, 256, 32, 2, 5, 3), (3, 3, 7, 5, 2, 2, 2))
+             (1, 1, 256, 32, 2, 5, 3), (3, 3, 7, 5, 2, 2, 2), (3, 9, 64, 64, 4, 16, 16))
     for (G, H, dk, dv, taps, ra, rg) in sizes:
+        if chunked and not ops.delta_chunked_takes(G, H, dk, dv, taps):
+            continue
         C = 2 * G * dk + H * dv
         N = C + H + ra + rg
-        lens1, lens2, slots = [70, 1, 19, 0], [1, 97, 2, 0], [3, 0, 2, -1]
+        lens1, lens2, slots = ([70, 1, 128, 0], [1, 97, 64, 0], [3, 0, 2, -1]) if chunked else ([70, 1, 19, 0], [1, 97, 2, 0], [3, 0, 2, -1])
         conv = rng.standard_normal((C, taps)) * 0.6
         a_log, dt_bias, nw = rng.standard_normal(H) - 1, rng.standard_normal(H * dk) * 2, 1 + 0.1 * rng.standard_normal(dv)
         a2, g2 = rng.standard_normal((H * dk, ra)) * 2, rng.standard_normal((H * dv, rg))
@@ -365,7 +368,8 @@ def test_the_channel_delta_kernels_against_the_recurrence_written_out():
                                    torch.tensor(slots, dtype=torch.int32, device="cuda"), state,
                                    torch.empty(T, ops.channel_delta_prep_width(G, H, dk, dv), device="cuda"),
                                    torch.empty(ops.channel_delta_group_floats(T, H, dk), device="cuda"), torch.empty(T, H * dv, device="cuda"),
-                                   out, G, H, dk, dv, taps)
+                                   out, G, H, dk, dv, taps,
+                                   chunk_scratch=torch.empty(ops.channel_delta_chunked_scratch_floats(T, len(lens), H, dk, dv), device="cuda") if chunked else None)
             o = out.cpu().numpy()
             at = 0
             for i, n in enumerate(lens[:3]):

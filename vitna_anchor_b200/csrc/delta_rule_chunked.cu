@@ -13,6 +13,14 @@
 // mixer, and the sums are of float32 values.  The results equal the token-by-token recurrence up to the order of sums.
 // A chunk that reaches past its segment's end is filled with tokens that do nothing.  Inputs are the rows `delta_prepare`
 // writes (q | k | v | log decay | beta).
+//
+// The form with a decay per head AND key channel (template flag CH; inputs are the rows `cdelta_prepare` writes, q | k | v | log
+// decay [H][dk] | beta [H] | ..): L_t is a vector over the key channels, and the decays no longer leave the sums over dk:
+//     A[t][i] = beta_t sum_d k_t[d] k_i[d] e^(L_t[d] - L_i[d]),     P[t][i] = sum_d q_t[d] k_i[d] e^(L_t[d] - L_i[d])
+// (an exponential per pair and channel; for pieces below the diagonal it is split as e^(L_t - r) e^(r - L_i) with r = L of the
+// piece's last column token, both factors at most 1, which makes eight exponentials a channel for a 4 x 4 piece instead of sixteen),
+// W and Qg carry e^(L_t[d]), KgT carries e^(L_C[d] - L_i[d]), and the state's rows decay by the vector e^(L_C[d]), which follows
+// U' in the scratch.  Everything else, the triangular solve and the scan included, is the same code.
 #include "common.cuh"
 
 namespace vk {
@@ -39,10 +47,13 @@ __device__ __forceinline__ bool find_chunk(const int32_t* seg_starts, int segmen
 }
 
 // Floats of scratch for one (chunk, head):  W [C][dk] | Qg [C][dk] | KgT [dk][C] | P [C][C] | U' [C][dv] | e^(L_C) and padding [4]
-__host__ __device__ __forceinline__ size_t dc_stride(int C, int dk, int dv) { return (size_t)C * (3 * dk + C + dv) + 4; }
+// (with a decay per channel: e^(L_C[d]) for every d, padded to a multiple of four)
+__host__ __device__ __forceinline__ size_t dc_stride(int C, int dk, int dv, bool ch = false) {
+    return (size_t)C * (3 * dk + C + dv) + (ch ? (dk + 3) / 4 * 4 : 4);
+}
 
 // grid (chunks of the step, H); 256 threads = a 16 x 16 arrangement for the products.
-template <int C>
+template <int C, bool CH>
 __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const float* __restrict__ prep, int P, const int32_t* __restrict__ seg_starts,
                                                                          const int32_t* __restrict__ seg_slots, int segments,
                                                                          float* __restrict__ scratch, int G, int H, int dk, int dv) {
@@ -68,11 +79,18 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
     float* A_s = q_s + C * ldk;            // [C][C+1]
     float* P_s = A_s + C * ldc;            // [C][C+1]
     float* x_s = P_s + C * ldc;            // [C][dv + dk]: the right sides, then the solutions
+    float* Lv = x_s + C * nr;              // CH: [C][dk+1], the decays' logarithms of every channel, then their running sums
 
     if (tid < C) {
         const bool on = tid < cn;
-        L[tid] = on ? prep[(size_t)(start + c0 + tid) * P + Cq + h] : 0.0f;
-        beta[tid] = on ? prep[(size_t)(start + c0 + tid) * P + Cq + H + h] : 0.0f;
+        if (!CH) L[tid] = on ? prep[(size_t)(start + c0 + tid) * P + Cq + h] : 0.0f;
+        beta[tid] = on ? prep[(size_t)(start + c0 + tid) * P + Cq + (CH ? H * dk : H) + h] : 0.0f;
+    }
+    if (CH) {
+        for (int e = tid; e < C * dk; e += DC_THREADS) {
+            const int t = e / dk, d = e - t * dk;
+            Lv[t * ldk + d] = t < cn ? prep[(size_t)(start + c0 + t) * P + Cq + (size_t)h * dk + d] : 0.0f;
+        }
     }
     for (int e = tid; e < C * dk; e += DC_THREADS) {
         const int t = e / dk, d = e - t * dk;
@@ -81,7 +99,12 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
         q_s[t * ldk + d] = t < cn ? row[(size_t)g * dk + d] : 0.0f;
     }
     __syncthreads();
-    if (tid == 0) {                         // the decays' logarithms summed up to each token
+    if (CH) {                               // the decays' logarithms summed up to each token, a channel a thread
+        for (int d = tid; d < dk; d += DC_THREADS) {
+            float acc = 0.0f;
+            for (int t = 0; t < C; t++) { acc += Lv[t * ldk + d]; Lv[t * ldk + d] = acc; }
+        }
+    } else if (tid == 0) {
         float acc = 0.0f;
         for (int t = 0; t < C; t++) { acc += L[t]; L[t] = acc; }
     }
@@ -90,7 +113,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
         const int t = e / nr, c = e - t * nr;
         float v = 0.0f;
         if (t < cn) v = c < dv ? beta[t] * prep[(size_t)(start + c0 + t) * P + 2 * G * dk + (size_t)h * dv + c]
-                               : beta[t] * expf(L[t]) * k_s[t * ldk + (c - dv)];
+                               : beta[t] * expf(CH ? Lv[t * ldk + (c - dv)] : L[t]) * k_s[t * ldk + (c - dv)];
         x_s[e] = v;
     }
     // k k^T and q k^T in 4 x 4 pieces: thread (ty, tx) has rows ty*4.., columns tx*4.. (C = 64: one piece a thread; C = 32: a quarter idle)
@@ -111,6 +134,30 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
                         qt[a] = q_s[(ty * 4 + a) * ldk + d];
                         ki[a] = k_s[(tx * 4 + a) * ldk + d];
                     }
+                    if (CH && tx == ty) {   // a piece on the diagonal: the exponent of every pair by itself (pairs above the diagonal: none)
+                        float lt[4];
+#pragma unroll
+                        for (int a = 0; a < 4; a++) lt[a] = Lv[(ty * 4 + a) * ldk + d];
+#pragma unroll
+                        for (int a = 0; a < 4; a++)
+#pragma unroll
+                            for (int b = 0; b < 4; b++) {
+                                const float w = b <= a ? expf(lt[a] - lt[b]) * ki[b] : 0.0f;
+                                kk[a][b] = fmaf(kt[a], w, kk[a][b]);
+                                qk[a][b] = fmaf(qt[a], w, qk[a][b]);
+                            }
+                        continue;
+                    }
+                    if (CH) {               // below the diagonal: every row token comes after every column token; both factors <= 1
+                        const float ref = Lv[(tx * 4 + 3) * ldk + d];
+#pragma unroll
+                        for (int a = 0; a < 4; a++) {
+                            const float et = expf(Lv[(ty * 4 + a) * ldk + d] - ref);
+                            kt[a] *= et;
+                            qt[a] *= et;
+                            ki[a] *= expf(ref - Lv[(tx * 4 + a) * ldk + d]);
+                        }
+                    }
 #pragma unroll
                     for (int a = 0; a < 4; a++)
 #pragma unroll
@@ -125,7 +172,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
 #pragma unroll
                 for (int b = 0; b < 4; b++) {
                     const int t = ty * 4 + a, i = tx * 4 + b;
-                    const float ratio = i <= t ? expf(L[t] - L[i]) : 0.0f;
+                    const float ratio = i <= t ? (CH ? 1.0f : expf(L[t] - L[i])) : 0.0f;
                     A_s[t * ldc + i] = i < t ? beta[t] * ratio * kk[a][b] : 0.0f;
                     P_s[t * ldc + i] = ratio * qk[a][b];
                 }
@@ -146,31 +193,33 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
         }
     }
     __syncthreads();
-    float* out = scratch + ((size_t)blockIdx.x * H + h) * dc_stride(C, dk, dv);
+    float* out = scratch + ((size_t)blockIdx.x * H + h) * dc_stride(C, dk, dv, CH);
     float* W_g = out;
     float* Q_g = W_g + C * dk;
     float* K_g = Q_g + C * dk;             // transposed: [dk][C]
     float* P_g = K_g + C * dk;
     float* U_g = P_g + C * C;
-    const float LC = L[C - 1];
+    const float LC = CH ? 0.0f : L[C - 1];
     for (int e = tid; e < C * dk; e += DC_THREADS) {
         const int t = e / dk, d = e - t * dk;
         W_g[e] = x_s[t * nr + dv + d];
-        Q_g[e] = expf(L[t]) * q_s[t * ldk + d];
+        Q_g[e] = expf(CH ? Lv[t * ldk + d] : L[t]) * q_s[t * ldk + d];
     }
     for (int e = tid; e < dk * C; e += DC_THREADS) {
         const int d = e / C, i = e - d * C;
-        K_g[e] = expf(LC - L[i]) * k_s[i * ldk + d];
+        K_g[e] = expf(CH ? Lv[(C - 1) * ldk + d] - Lv[i * ldk + d] : LC - L[i]) * k_s[i * ldk + d];
     }
     for (int e = tid; e < C * C; e += DC_THREADS) P_g[e] = P_s[(e / C) * ldc + e % C];
     for (int e = tid; e < C * dv; e += DC_THREADS) U_g[e] = x_s[(e / dv) * nr + e % dv];
-    if (tid == 0) U_g[C * dv] = expf(LC);
+    if (CH) {
+        for (int d = tid; d < dk; d += DC_THREADS) U_g[C * dv + d] = expf(Lv[(C - 1) * ldk + d]);
+    } else if (tid == 0) U_g[C * dv] = expf(LC);
 }
 
 // grid (segments, H, column slices); 256 threads; COLS columns of the state a block.  A chunk's operands arrive by cp.async in one of
 // two buffers, a chunk ahead.
-template <int C, int COLS>
-__global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __restrict__ scratch, const float* __restrict__ proj,
+template <int C, int COLS, bool CH>
+__global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __restrict__ scratch, const float* __restrict__ proj, int N,
                                                                const int32_t* __restrict__ seg_starts, const int32_t* __restrict__ seg_slots,
                                                                float* __restrict__ state, size_t state_stride, size_t conv_off,
                                                                float* __restrict__ o, int G, int H, int dk, int dv, int taps) {
@@ -182,8 +231,8 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __re
     const int start = seg_starts[seg], n = seg_starts[seg + 1] - start;
     int base = 0;                                            // the step's chunk number of this segment's first chunk
     for (int s = 0; s < seg; s++) base += (seg_starts[s + 1] - seg_starts[s] + C - 1) / C;
-    const int Cq = 2 * G * dk + H * dv, N = Cq + H * dv + 2 * H;
-    const size_t stride = dc_stride(C, dk, dv);
+    const int Cq = 2 * G * dk + H * dv;                     // N: floats of a row of proj
+    const size_t stride = dc_stride(C, dk, dv, CH);
     const int c = tid % COLS, r0 = tid / COLS, col = part * COLS + c;
     const bool live = col < dv;
     float* row = state + (size_t)slot * state_stride;
@@ -217,7 +266,12 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __re
         float up[C / RG];                                    // U' of this thread's places
 #pragma unroll
         for (int j = 0; j < C / RG; j++) up[j] = live ? U_g[(size_t)(r0 + RG * j) * dv + col] : 0.0f;
-        const float gC = U_g[(size_t)C * dv];
+        const float gC = CH ? 0.0f : U_g[(size_t)C * dv];
+        float gv[DC_MAX_DK / RG];                            // CH: the chunk's decay of each of this thread's rows of the state
+        if (CH) {
+#pragma unroll
+            for (int j = 0; j < DC_MAX_DK / RG; j++) gv[j] = r0 + RG * j < dk ? U_g[(size_t)C * dv + r0 + RG * j] : 0.0f;
+        }
         asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
         // W S and Qg S together: the state's values are loaded once for both
@@ -273,7 +327,7 @@ __global__ void __launch_bounds__(256) delta_chunk_scan_kernel(const float* __re
 #pragma unroll
         for (int j = 0; j < DC_MAX_DK / RG; j++) {
             const int d = r0 + RG * j;
-            if (d < dk) S_s[c * lds + d] = fmaf(gC, S_s[c * lds + d], s_new[j]);
+            if (d < dk) S_s[c * lds + d] = fmaf(CH ? gv[j] : gC, S_s[c * lds + d], s_new[j]);
         }
     }
     __syncthreads();
@@ -319,32 +373,54 @@ VK_API size_t vk_delta_chunked_scratch_bytes(int tokens, int segments, int H, in
     return ((size_t)tokens / C + segments + 1) * H * dc_stride(C, dk, dv) * sizeof(float);
 }
 
-// prep [tokens][prep width] as delta_prepare leaves it; proj as for the token-by-token kernel; o [tokens][H*dv] float32.
-VK_API int vk_delta_chunked(const float* prep, int prep_width, const float* proj, const int32_t* seg_starts, const int32_t* seg_slots, float* state,
-                            size_t state_stride, float* o, float* scratch, int segments, int tokens, int G, int H, int dk, int dv, int taps,
-                            cudaStream_t stream) {
+template <bool CH>
+static int delta_chunked_launch(const float* prep, int prep_width, const float* proj, int proj_width, const int32_t* seg_starts,
+                                const int32_t* seg_slots, float* state, size_t state_stride, float* o, float* scratch, int segments, int tokens,
+                                int G, int H, int dk, int dv, int taps, cudaStream_t stream) {
     if (segments <= 0 || tokens <= 0) return VK_OK;
     if (!vk_delta_chunked_takes(G, H, dk, dv, taps)) return VK_BAD_SHAPE;
     if (((uintptr_t)scratch % 16) || H > 65535) return VK_BAD_ALIGNMENT;
     const int C = dc_chunk(dk);
     const int chunks = tokens / C + segments;
-    const size_t smem1 = (size_t)(2 * C * (dk + 1) + 2 * C * (C + 1) + C * (dv + dk)) * sizeof(float);
+    const size_t smem1 = (size_t)(2 * C * (dk + 1) + 2 * C * (C + 1) + C * (dv + dk) + (CH ? C * (dk + 1) : 0)) * sizeof(float);
     constexpr int COLS = 16;
     const size_t smem2 = (size_t)(COLS * (dk + 4) + COLS * (C + 4) + 2 * C * (3 * dk + C)) * sizeof(float);
     const int parts = (dv + COLS - 1) / COLS;
     if (smem1 > 200 * 1024 || smem2 > 200 * 1024) return VK_TOO_LARGE;
 #define GO(CC)                                                                                                                             \
     {                                                                                                                                      \
-        auto k1 = delta_chunk_prepare_kernel<CC>;                                                                                          \
-        auto k2 = delta_chunk_scan_kernel<CC, COLS>;                                                                                       \
+        auto k1 = delta_chunk_prepare_kernel<CC, CH>;                                                                                      \
+        auto k2 = delta_chunk_scan_kernel<CC, COLS, CH>;                                                                                   \
         cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);                                                 \
         cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);                                                 \
         int rc = launch_plain(k1, dim3(chunks, H), dim3(DC_THREADS), smem1, stream, prep, prep_width, seg_starts, seg_slots, segments,    \
                               scratch, G, H, dk, dv);                                                                                      \
         if (rc != 0) return rc;                                                                                                            \
-        return launch_plain(k2, dim3(segments, H, parts), dim3(256), smem2, stream, (const float*)scratch, proj, seg_starts, seg_slots,  \
-                            state, state_stride, (size_t)H * dv * dk, o, G, H, dk, dv, taps);                                              \
+        return launch_plain(k2, dim3(segments, H, parts), dim3(256), smem2, stream, (const float*)scratch, proj, proj_width, seg_starts,  \
+                            seg_slots, state, state_stride, (size_t)H * dv * dk, o, G, H, dk, dv, taps);                                   \
     }
     if (C == 64) GO(64) else GO(32)
 #undef GO
+}
+
+// prep [tokens][prep width] as delta_prepare leaves it; proj as for the token-by-token kernel; o [tokens][H*dv] float32.
+VK_API int vk_delta_chunked(const float* prep, int prep_width, const float* proj, const int32_t* seg_starts, const int32_t* seg_slots, float* state,
+                            size_t state_stride, float* o, float* scratch, int segments, int tokens, int G, int H, int dk, int dv, int taps,
+                            cudaStream_t stream) {
+    return delta_chunked_launch<false>(prep, prep_width, proj, 2 * G * dk + 2 * H * dv + 2 * H, seg_starts, seg_slots, state, state_stride, o,
+                                       scratch, segments, tokens, G, H, dk, dv, taps, stream);
+}
+
+// The form with a decay per head and key channel: prep as cdelta_prepare leaves it, proj rows of proj_width floats (the
+// convolution's inputs first).  The sizes are those vk_delta_chunked_takes.
+VK_API size_t vk_cdelta_chunked_scratch_bytes(int tokens, int segments, int H, int dk, int dv) {
+    const int C = dc_chunk(dk);
+    return ((size_t)tokens / C + segments + 1) * H * dc_stride(C, dk, dv, true) * sizeof(float);
+}
+
+VK_API int vk_cdelta_chunked(const float* prep, int prep_width, const float* proj, int proj_width, const int32_t* seg_starts,
+                             const int32_t* seg_slots, float* state, size_t state_stride, float* o, float* scratch, int segments, int tokens,
+                             int G, int H, int dk, int dv, int taps, cudaStream_t stream) {
+    return delta_chunked_launch<true>(prep, prep_width, proj, proj_width, seg_starts, seg_slots, state, state_stride, o, scratch, segments,
+                                      tokens, G, H, dk, dv, taps, stream);
 }

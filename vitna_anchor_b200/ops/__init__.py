@@ -1099,6 +1099,12 @@ def channel_delta_group_floats(tokens: int, H: int, dk: int) -> int:
     return tokens * H * (4 * ((dk + 3) // 4 * 4) + 8)
 
 
+def channel_delta_chunked_scratch_floats(tokens: int, segments: int, H: int, dk: int, dv: int) -> int:
+    fn = lib().vk_cdelta_chunked_scratch_bytes
+    fn.restype = ctypes.c_size_t
+    return int(fn(tokens, segments, H, dk, dv)) // 4
+
+
 def channel_delta_decode_takes(G: int, H: int, dk: int, dv: int, taps: int, ra: int, rg: int) -> bool:
     """Whether the one-kernel form for single decoded tokens takes these sizes (key size a multiple of 4 up to 512)."""
     return bool(lib().vk_cdelta_decode_takes(G, H, dk, dv, taps, ra, rg))
@@ -1107,14 +1113,17 @@ def channel_delta_decode_takes(G: int, H: int, dk: int, dv: int, taps: int, ra: 
 def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor, a2t: torch.Tensor,
                        g2t: torch.Tensor, norm_w: torch.Tensor, eps: float, token_seg: torch.Tensor, seg_starts: torch.Tensor,
                        seg_slots: torch.Tensor, state: torch.Tensor, prep: torch.Tensor, groups: torch.Tensor, o: torch.Tensor, out: torch.Tensor,
-                       G: int, H: int, dk: int, dv: int, taps: int, single_tokens: bool = False) -> torch.Tensor:
+                       G: int, H: int, dk: int, dv: int, taps: int, single_tokens: bool = False,
+                       chunk_scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The delta rule whose decay differs by head and key channel, from the projections to the input of the output projection.
     proj float32 [T, 2 G dk + H dv + H + ra + rg] = q | k | v | b | a1 | g1;  a2t float32 [ra, H dk] and g2t [rg, H dv], the wide
     halves of the two low-rank projections, transposed;  dt_bias [H dk];  a_log [H];  norm_w [dv];  state float32
     [slots, delta_state_floats];  prep [T, channel_delta_prep_width], groups (flat, channel_delta_group_floats(T, H, dk)) and o [T, H dv]
     float32 scratch;  out [T, H dv] in the compute dtype.  Four launches: prepare, what the groups of tokens need besides the state
-    (all groups side by side), the recurrence (which also writes the state), gate.  With single_tokens (every segment is one
-    token; sizes that channel_delta_decode_takes) everything is ONE launch."""
+    (all groups side by side), the recurrence (which also writes the state), gate.  With chunk_scratch (float32,
+    channel_delta_chunked_scratch_floats(T, segments, ...); sizes that delta_chunked_takes) the recurrence runs in its chunked form
+    instead: what does not need the state for all chunks side by side, then the chunks of every request in order.  With
+    single_tokens (every segment is one token; sizes that channel_delta_decode_takes) everything is ONE launch."""
     C = 2 * G * dk + H * dv
     for name, t, d in (("proj", proj, 2), ("conv_w", conv_w, 2), ("a_log", a_log, 1), ("dt_bias", dt_bias, 1), ("a2t", a2t, 2), ("g2t", g2t, 2),
                        ("norm_w", norm_w, 1), ("state", state, 2), ("prep", prep, 2), ("o", o, 2), ("groups", groups, 1)):
@@ -1137,10 +1146,17 @@ def channel_delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Te
         return out
     _check(lib().vk_cdelta_prepare(_p(proj), _p(conv_w), _p(a_log), _p(dt_bias), _p(a2t), _p(g2t), _p(token_seg), _p(seg_starts), _p(seg_slots),
                                    _p(state), stride, _p(prep), T, G, H, dk, dv, taps, ra, rg, _stream()), "cdelta_prepare")
-    _check(lib().vk_cdelta_recurrence(_p(prep), _p(proj), proj.shape[1], _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
-                                      _p(groups), _p(o), S, T, G, H, dk, dv, taps, _stream()), "cdelta_recurrence")
     global _launches
-    _launches += 1                                  # two kernels
+    if chunk_scratch is not None:
+        _req(chunk_scratch, "chunk_scratch", torch.float32, 1)
+        if chunk_scratch.numel() < channel_delta_chunked_scratch_floats(T, S, H, dk, dv):
+            raise KernelError("channel_delta_rule: the scratch of the chunked form is too small")
+        _check(lib().vk_cdelta_chunked(_p(prep), prep.shape[1], _p(proj), proj.shape[1], _p(seg_starts), _p(seg_slots), _p(state), stride, _p(o),
+                                       _p(chunk_scratch), S, T, G, H, dk, dv, taps, _stream()), "cdelta_chunked")
+    else:
+        _check(lib().vk_cdelta_recurrence(_p(prep), _p(proj), proj.shape[1], _p(token_seg), _p(seg_starts), _p(seg_slots), _p(state), stride,
+                                          _p(groups), _p(o), S, T, G, H, dk, dv, taps, _stream()), "cdelta_recurrence")
+    _launches += 1                                  # two kernels either way
     _check(lib().vk_cdelta_gate(_p(o), _p(prep), _p(norm_w), ctypes.c_float(eps), _p(out), T, G, H, dk, dv, _dt(out), _stream()), "cdelta_gate")
     return out
 

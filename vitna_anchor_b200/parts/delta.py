@@ -117,12 +117,17 @@ class ChannelDeltaRule(Mixer):
             raise ValueError("a recurrent mixer has no cache that another run could read")
         T, ws = ctx.num_tokens, ctx.workspace
         proj = ops.linear(xn, self.w_in, ws.rows("cdelta.proj", T, self.w_in.shape[0], torch.float32), ops.LINEAR_F32)
+        serving = not (ctx.dtype == torch.float32 and ops.float32_exact())
+        # a prompt's step takes the chunked form (the exact 32-bit routing keeps one set of kernels for every step)
+        scratch = None
+        if T > GatedDeltaRule.CHUNKED_FROM and serving and ops.delta_chunked_takes(self.G, self.H, self.dk, self.dv, self.taps):
+            scratch = ws.flat(f"cdelta.chunks/{self.H}/{self.dk}/{self.dv}",
+                              ops.channel_delta_chunked_scratch_floats(ws.max_tokens, ws.max_segments, self.H, self.dk, self.dv), torch.float32)
         out = ops.channel_delta_rule(proj, self.conv, self.a_log, self.dt_bias, self.a2t, self.g2t, self.norm_weight, self.eps, ctx.token_seg,
                                      ctx.seg_starts, ctx.seg_slots, cache.state,
                                      ws.rows("cdelta.prep", T, ops.channel_delta_prep_width(self.G, self.H, self.dk, self.dv), torch.float32),
                                      ws.flat(f"cdelta.groups/{self.H}/{self.dk}", ops.channel_delta_group_floats(ws.max_tokens, self.H, self.dk),
                                              torch.float32),
                                      ws.rows("delta.o", T, self.H * self.dv, torch.float32), ws.rows("delta.out", T, self.H * self.dv, ctx.dtype),
-                                     self.G, self.H, self.dk, self.dv, self.taps,
-                                     single_tokens=ctx.decode_only and not (ctx.dtype == torch.float32 and ops.float32_exact()))
+                                     self.G, self.H, self.dk, self.dv, self.taps, single_tokens=ctx.decode_only and serving, chunk_scratch=scratch)
         ops.linear(out, self.wo, residual, ops.LINEAR_ACC_F32)
