@@ -17,8 +17,9 @@
 // The form with a decay per head AND key channel (template flag CH; inputs are the rows `cdelta_prepare` writes, q | k | v | log
 // decay [H][dk] | beta [H] | ..): L_t is a vector over the key channels, and the decays no longer leave the sums over dk:
 //     A[t][i] = beta_t sum_d k_t[d] k_i[d] e^(L_t[d] - L_i[d]),     P[t][i] = sum_d q_t[d] k_i[d] e^(L_t[d] - L_i[d])
-// (an exponential per pair and channel; for pieces below the diagonal it is split as e^(L_t - r) e^(r - L_i) with r = L of the
-// piece's last column token, both factors at most 1, which makes eight exponentials a channel for a 4 x 4 piece instead of sixteen),
+// (an exponential per pair and channel; for 4 x 4 pieces below the diagonal it is split as e^(L_t - r) e^(r - L_i) with r = L of the
+// piece's last column token, both factors at most 1, which makes eight exponentials a channel for a piece instead of sixteen; a piece's
+// channels are shared out over two to eight threads),
 // W and Qg carry e^(L_t[d]), KgT carries e^(L_C[d] - L_i[d]), and the state's rows decay by the vector e^(L_C[d]), which follows
 // U' in the scratch.  Everything else, the triangular solve and the scan included, is the same code.
 #include "common.cuh"
@@ -116,6 +117,75 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
                                : beta[t] * expf(CH ? Lv[t * ldk + (c - dv)] : L[t]) * k_s[t * ldk + (c - dv)];
         x_s[e] = v;
     }
+    if (CH) {
+        // k k^T and q k^T with the pairs' decays, in 4 x 4 pieces.  The exponentials make a piece expensive, so the channels of a
+        // piece are shared out: the threads that would have a piece above the diagonal take half of the channels of the piece
+        // mirrored below it, and with C = 32 (a quarter as many pieces as threads) every piece's channels are cut in four again.
+        // The parts of a piece are added in a fixed order, one barrier a part.
+        constexpr int NB = C / 4, NPC = NB * NB, S = DC_THREADS / NPC;
+        for (int e = tid; e < C * ldc; e += DC_THREADS) { A_s[e] = 0.0f; P_s[e] = 0.0f; }
+        const int piece = tid % NPC, dsplit = tid / NPC;
+        int ty = piece / NB, tx = piece % NB;
+        const bool mirror = tx > ty;
+        if (mirror) { const int z = ty; ty = tx; tx = z; }
+        const bool diag = tx == ty;
+        const int parts = diag ? S : 2 * S, part = diag ? dsplit : dsplit * 2 + (mirror ? 1 : 0);
+        float kk[4][4], qk[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+            for (int b = 0; b < 4; b++) kk[a][b] = qk[a][b] = 0.0f;
+        for (int d = part * dk / parts; d < (part + 1) * dk / parts; d++) {
+            float kt[4], qt[4], ki[4], lt[4], li[4];
+#pragma unroll
+            for (int a = 0; a < 4; a++) {
+                kt[a] = k_s[(ty * 4 + a) * ldk + d];
+                qt[a] = q_s[(ty * 4 + a) * ldk + d];
+                ki[a] = k_s[(tx * 4 + a) * ldk + d];
+                lt[a] = Lv[(ty * 4 + a) * ldk + d];
+                li[a] = Lv[(tx * 4 + a) * ldk + d];
+            }
+            if (diag) {                     // the exponent of every pair by itself: six below the diagonal, none on or above it
+#pragma unroll
+                for (int a = 0; a < 4; a++)
+#pragma unroll
+                    for (int b = 0; b <= a; b++) {
+                        const float w = b < a ? expf(lt[a] - lt[b]) * ki[b] : ki[b];
+                        kk[a][b] = fmaf(kt[a], w, kk[a][b]);
+                        qk[a][b] = fmaf(qt[a], w, qk[a][b]);
+                    }
+            } else {                        // every row token comes after every column token: e^(L_t - r) e^(r - L_i), r = L of the last
+                const float ref = li[3];    // column token, both factors at most 1
+#pragma unroll
+                for (int a = 0; a < 4; a++) {
+                    const float et = expf(lt[a] - ref);
+                    kt[a] *= et;
+                    qt[a] *= et;
+                    ki[a] *= expf(ref - li[a]);
+                }
+#pragma unroll
+                for (int a = 0; a < 4; a++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        kk[a][b] = fmaf(kt[a], ki[b], kk[a][b]);
+                        qk[a][b] = fmaf(qt[a], ki[b], qk[a][b]);
+                    }
+            }
+        }
+        for (int ph = 0; ph < 2 * S; ph++) {
+            __syncthreads();
+            if (part == ph) {
+#pragma unroll
+                for (int a = 0; a < 4; a++)
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        const int t = ty * 4 + a, i = tx * 4 + b;
+                        if (i < t) A_s[t * ldc + i] += beta[t] * kk[a][b];
+                        if (i <= t) P_s[t * ldc + i] += qk[a][b];
+                    }
+            }
+        }
+    } else
     // k k^T and q k^T in 4 x 4 pieces: thread (ty, tx) has rows ty*4.., columns tx*4.. (C = 64: one piece a thread; C = 32: a quarter idle)
     {
         const int ty = tid / 16, tx = tid % 16;
@@ -134,30 +204,6 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
                         qt[a] = q_s[(ty * 4 + a) * ldk + d];
                         ki[a] = k_s[(tx * 4 + a) * ldk + d];
                     }
-                    if (CH && tx == ty) {   // a piece on the diagonal: the exponent of every pair by itself (pairs above the diagonal: none)
-                        float lt[4];
-#pragma unroll
-                        for (int a = 0; a < 4; a++) lt[a] = Lv[(ty * 4 + a) * ldk + d];
-#pragma unroll
-                        for (int a = 0; a < 4; a++)
-#pragma unroll
-                            for (int b = 0; b < 4; b++) {
-                                const float w = b <= a ? expf(lt[a] - lt[b]) * ki[b] : 0.0f;
-                                kk[a][b] = fmaf(kt[a], w, kk[a][b]);
-                                qk[a][b] = fmaf(qt[a], w, qk[a][b]);
-                            }
-                        continue;
-                    }
-                    if (CH) {               // below the diagonal: every row token comes after every column token; both factors <= 1
-                        const float ref = Lv[(tx * 4 + 3) * ldk + d];
-#pragma unroll
-                        for (int a = 0; a < 4; a++) {
-                            const float et = expf(Lv[(ty * 4 + a) * ldk + d] - ref);
-                            kt[a] *= et;
-                            qt[a] *= et;
-                            ki[a] *= expf(ref - Lv[(tx * 4 + a) * ldk + d]);
-                        }
-                    }
 #pragma unroll
                     for (int a = 0; a < 4; a++)
 #pragma unroll
@@ -172,7 +218,7 @@ __global__ void __launch_bounds__(DC_THREADS) delta_chunk_prepare_kernel(const f
 #pragma unroll
                 for (int b = 0; b < 4; b++) {
                     const int t = ty * 4 + a, i = tx * 4 + b;
-                    const float ratio = i <= t ? (CH ? 1.0f : expf(L[t] - L[i])) : 0.0f;
+                    const float ratio = i <= t ? expf(L[t] - L[i]) : 0.0f;
                     A_s[t * ldc + i] = i < t ? beta[t] * ratio * kk[a][b] : 0.0f;
                     P_s[t * ldc + i] = ratio * qk[a][b];
                 }
