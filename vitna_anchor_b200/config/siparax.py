@@ -155,8 +155,8 @@ class SiparaxConfig:
                 src = layers[m.kv_from].mixer if m.kv_from < i else None
                 if not isinstance(src, LatentSpec) or src.kv_from is not None:
                     raise ConfigError(f"config.json: layers[{i}].mixer.kv_from does not name an earlier latent attention layer with rows of its own")
-                if (src.kv_rank, src.rot_dim, src.rot, src.interleaved) != (m.kv_rank, m.rot_dim, m.rot, m.interleaved):
-                    raise ConfigError(f"config.json: layers[{i}] and the layer it reads rows from differ in kv_rank, rot_dim or rotation")
+                if (src.kv_rank, src.rot_dim) != (m.kv_rank, m.rot_dim):      # the rows are read as that layer wrote them; this layer's
+                    raise ConfigError(f"config.json: layers[{i}] and the layer it reads rows from differ in kv_rank or rot_dim")     # own rotation turns its queries
         eps = _number(cfg["norm"], "eps", "norm.")
         if eps < 0:
             raise ConfigError("config.json: norm.eps is negative")
