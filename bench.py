@@ -581,7 +581,7 @@ SIPARAX_RANK = 16           # what random initialisation takes for the ranks of 
 
 
 def siparax_config(sz):
-    rot = dict(base=10000.0, dims=sz["rot_dim"], scaling=dict(factor=8.0, original=2048, fast=32.0, slow=1.0))
+    rot = dict(base=100000.0, dims=sz["rot_dim"], scaling=dict(factor=4.0, original=1024, fast=24.0, slow=2.0))
     att = dict(heads=sz["heads"], dim=sz["dim"], rot_dim=sz["rot_dim"], vdim=sz["vdim"], kv_rank=sz["kv_rank"], q_rank=sz["q_rank"],
                scale=(sz["dim"] + sz["rot_dim"]) ** -0.5, rot=rot)
     dl = dict(heads=sz["heads"], kv_heads=sz["kv"], dim=sz["dim"], vdim=sz["vdim"], conv=4)

@@ -38,7 +38,7 @@ def test_what_the_reader_does_not_know_is_refused():
             SiparaxConfig.from_dict(c)
 
 
-@pytest.mark.parametrize("r", [SM.ROT_A, SM.ROT_B, SM.rot(50.0, 4), SM.rot(500000.0, 64, (8.0, 2048, 32.0, 1.0)), SM.rot(10000.0, 2, (3.0, 16, 1.0, 1.0))])
+@pytest.mark.parametrize("r", [SM.ROT_A, SM.ROT_B, SM.rot(50.0, 4), SM.rot(1000000.0, 64, (16.0, 4096, 24.0, 2.0)), SM.rot(10000.0, 2, (3.0, 16, 1.0, 1.0))])
 def test_the_rotation_frequencies(r):
     sc = r.get("scaling")
     f, mag = blended_frequencies(r["base"], r["dims"], None if sc is None else (sc["factor"], sc["original"], sc["fast"], sc["slow"]))
