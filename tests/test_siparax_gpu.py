@@ -85,6 +85,7 @@ ALONE = {
     "latent_neighbours": SM.config(40, 32, [SM.layer("latent_attention", SM.latent(2, 16, 8, 8, 24, 16, 0.4, R1))]),
     "latent_halves_gated": SM.config(40, 32, [SM.layer("latent_attention_2", SM.latent(3, 8, 16, 24, 16, 20, 0.3, R2))]),
     "latent_part_turned": SM.config(40, 32, [SM.layer("latent_attention_2", SM.latent(2, 8, 16, 8, 16, 8, 0.3, SM.rot(30.0, 6)))]),
+    "latent_tensor_core_sizes": SM.config(40, 64, [SM.layer("latent_attention_2", SM.latent(4, 16, 32, 16, 64, 32, 0.2, SM.rot(1000.0, 32, (2.0, 32, 8.0, 1.0))))]),
     "latent_odd": SM.config(40, 24, [SM.layer("latent_attention", SM.latent(1, 7, 2, 5, 9, 11, 0.5, SM.rot(20.0, 2, (2.0, 8, 2.0, 1.0))))]),
     "latent_shared_rows": SM.config(40, 32, [SM.layer("latent_attention_2", SM.latent(2, 8, 8, 8, 24, 16, 0.4, R1)),
                                              SM.layer("latent_attention_2", SM.latent(4, 16, 8, 4, 24, 8, 0.2, R1, kv_from=0))]),
@@ -306,7 +307,7 @@ def test_latent_prepare_and_the_query_rotation(interleaved):
     pos = np.array([0, 1, 2, 17, 300, 4095, 65536, 99999, 5])
     slots = np.array([3, 27, 0, 9, -1, 14, 1, 20, 26])
     f = lambda a, dt=torch.float32: torch.tensor(np.asarray(a), dtype=dt, device="cuda")
-    cache = torch.zeros(pages, ps * (2 * r + rd), device="cuda")
+    cache = torch.zeros(pages, ps * (r + rd), device="cuda")
     cq = ops.latent_prepare(f(proj), qr, f(qw), torch.empty(T, qr, device="cuda"), 1e-5, f(pos, torch.int32), f(freq), mag, dims, interleaved,
                             kv_off=qr, kv_rank=r, rot_dim=rd, kv_norm_w=f(kw), slot_mapping=f(slots, torch.int32), cache_layer=cache, page_size=ps)
     assert np.abs(cq.cpu().numpy() - PS.rms(proj[:, :qr], 1e-5, qw)).max() < 1e-5
@@ -317,14 +318,14 @@ def test_latent_prepare_and_the_query_rotation(interleaved):
             continue
         kr = PS.rotate(proj[t:t + 1, qr + r:qr + r + rd], int(pos[t]), rot, pairing)[0]
         page, off = host[slots[t] // ps], slots[t] % ps
-        krow, vrow = page[off * (r + rd):(off + 1) * (r + rd)], page[ps * (r + rd) + off * r:ps * (r + rd) + (off + 1) * r]
-        assert np.abs(krow[:r] - c[t]).max() < 1e-5 and np.abs(vrow - c[t]).max() < 1e-5
+        krow = page[off * (r + rd):(off + 1) * (r + rd)]
+        assert np.abs(krow[:r] - c[t]).max() < 1e-5
         assert np.abs(krow[r:] - kr).max() < 2e-2 * (1 + pos[t] * 1e-5)      # float32 angles: the error grows with the position
         if pos[t] < 5000:
             assert np.abs(krow[r:] - kr).max() < 5e-4
     untouched = np.ones(pages * ps, bool)
     untouched[slots[slots >= 0]] = False
-    keys = host[:, :ps * (r + rd)].reshape(pages * ps, r + rd)
+    keys = host.reshape(pages * ps, r + rd)
     assert not keys[untouched].any()
     q = rng.standard_normal((T, H * (r + rd)))
     got = ops.latent_rotate_q(f(q), f(pos, torch.int32), f(freq), mag, H, r, rd, dims, interleaved).cpu().numpy().reshape(T, H, r + rd)
@@ -394,6 +395,46 @@ def test_the_channel_delta_kernels_against_the_recurrence_written_out(chunked):
                     want[t, h] = S.T @ q[t, h // (H // G)]
             want = (PS.rms(want, 1e-5, nw) * gate).reshape(len(p), H * dv)
             assert np.abs(np.concatenate(outs[i]) - want).max() < 2e-5 * max(1.0, np.abs(want).max()), (G, H, dk, dv, taps, i)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_values_inside_the_keys_give_what_values_beside_them_give(dtype):
+    """The three attention kernels on a cache of keys alone whose first vd values are the values, against the same kernels on a
+    cache that holds those values once more beside the keys: a prompt's portion far into its context and two decoded tokens."""
+    from vitna_anchor_b200 import ops
+    g = torch.Generator(device="cuda").manual_seed(3)
+    nh, hd, vd, ps, pages, scale = 4, 96, 64, 8, 40, 0.11
+    keys = (torch.randn(pages, ps, hd, generator=g, device="cuda") * 1.5).to(dtype)
+    inside = keys.reshape(pages, ps * hd).contiguous()
+    beside = torch.cat([keys.reshape(pages, ps * hd), keys[..., :vd].reshape(pages, ps * vd)], dim=1).contiguous()
+    perm = torch.randperm(pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    bt = torch.stack([perm[:20], perm[20:]]).contiguous().cuda()                  # two requests, 20 pages each
+    pos = list(range(100, 130)) + [159, 77]                                       # a portion of 30 tokens, then two single tokens
+    seg = [0] * 30 + [1, 0]
+    T = len(pos)
+    q = (torch.randn(T, nh * hd, generator=g, device="cuda")).to(dtype)
+    i32 = lambda a: torch.tensor(a, dtype=torch.int32, device="cuda")
+    positions, token_seg = i32(pos), i32(seg)
+    outs = {}
+    for name, cache, flag in (("inside", inside, True), ("beside", beside, False)):
+        rows = ops.attention_rows_biased(q, cache, bt, token_seg, positions, torch.zeros(T, nh * vd, dtype=dtype, device="cuda"), nh, 1, hd, vd, ps,
+                                         scale, v_in_key=flag)
+        dec = torch.zeros(T, nh * vd, dtype=dtype, device="cuda")
+        scratch = torch.zeros(ops.attention_decode_scratch_bytes(4, nh, 1, hd, 512), dtype=torch.uint8, device="cuda")
+        ops.attention_decode_biased(q, cache, bt, token_seg, positions, dec, scratch, 4, nh, 1, hd, vd, ps, scale, 512, 160, tok_list=i32([30, 31]),
+                                    v_in_key=flag)
+        outs[name] = [rows, dec[30:]]
+        if dtype == torch.bfloat16:
+            pre = torch.zeros(T, nh * vd, dtype=dtype, device="cuda")
+            ops.attention_prefill_biased(q, cache, bt, i32([[0, 30, 100, 0]]), pre, nh, 1, hd, vd, ps, scale, v_in_key=flag)
+            outs[name].append(pre[:30])
+    ops.check_device_errors()
+    for a, b in zip(outs["inside"], outs["beside"]):
+        assert torch.equal(a, b)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (outs["inside"][1].float() - outs["inside"][0][30:].float()).abs().max() < tol
+    if dtype == torch.bfloat16:
+        assert (outs["inside"][2].float() - outs["inside"][0][:30].float()).abs().max() < tol
 
 
 def test_the_one_kernel_channel_delta_rule_for_single_tokens_gives_what_the_other_kernels_give():

@@ -7,7 +7,8 @@ KVSpec form a group that shares page ids and has a pool of its own:
 
     pool[group]   [layers of the group, pages, 2 (k, v), kv heads, page_size, head_dim]
                   (values of another size than the keys: [layers, pages, kv heads * page_size * (head_dim + v_dim)],
-                  a page's keys [kv heads, page_size, head_dim] followed by its values [kv heads, page_size, v_dim])
+                  a page's keys [kv heads, page_size, head_dim] followed by its values [kv heads, page_size, v_dim];
+                  values inside the keys: [layers, pages, kv heads * page_size * head_dim])
     state[cache]  [max_requests, *shape]     one row per request slot
 
 A request holds one slot from open() to close(); its state rows are zeroed
@@ -26,11 +27,14 @@ from .pages import CacheError, OutOfPages, PageGroup, PageTables, UNMAPPED  # no
 @dataclass(frozen=True)
 class KVSpec:
     """Keys and values of `num_kv_heads` heads of `head_dim`; window = 0 keeps every position; v_dim = 0: values of
-    the keys' size, else their own size (a page then holds the keys of its slots followed by the values)."""
+    the keys' size, else their own size (a page then holds the keys of its slots followed by the values).
+    value_in_key: a key's first v_dim values ARE its value; the cache then holds the keys alone (a latent that is
+    read both as part of the key and as the value is stored once)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_dim: int = 0
+    value_in_key: bool = False
 
 
 @dataclass(frozen=True)
@@ -65,7 +69,7 @@ class CacheManager:
             if isinstance(spec, KVSpec):
                 by_spec.setdefault(spec, []).append(cid)
         self.groups = [PageGroup(tuple(ids), s.num_kv_heads, s.head_dim, s.window) for s, ids in by_spec.items()]
-        self._v_dims = [s.v_dim or s.head_dim for s in by_spec]
+        self._v_dims = [0 if s.value_in_key else (s.v_dim or s.head_dim) for s in by_spec]      # values stored beside the keys
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.groups)
         self.tables = PageTables(self.groups, page_size, list(num_pages), max_requests)
@@ -74,7 +78,7 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             pool = None
             if allocate:
-                shape = ((2, grp.num_kv_heads, page_size, grp.head_dim) if self._v_dims[g] == grp.head_dim
+                shape = ((2, grp.num_kv_heads, page_size, grp.head_dim) if self._v_dims[g] == grp.head_dim and not list(by_spec)[g].value_in_key
                          else (grp.num_kv_heads * page_size * (grp.head_dim + self._v_dims[g]),))
                 pool = torch.zeros((len(grp.cache_ids), self.tables.pools[g].num_pages, *shape), dtype=dtype, device=self.device)
             self.pools.append(pool)

@@ -60,7 +60,7 @@ template <int HD, int VD>
 __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache, const int32_t* __restrict__ block_tables,
     const int32_t* __restrict__ tiles, __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_blocks, float scale,
-    int window, const float* __restrict__ dist_bias, int max_dist) {
+    int window, const float* __restrict__ dist_bias, int max_dist, int v_in_key) {
     typedef __nv_bfloat16 T;
     constexpr int LD = HD + 8;                      // padded row: 16-byte shifts keep ldmatrix free of bank conflicts
     constexpr int LDV = VD + 8;
@@ -80,8 +80,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
     const int tid = threadIdx.x % PF_GROUP, warp = tid >> 5, lane = tid & 31;      // within the group
     const int g = lane >> 2, qd = lane & 3;
     const int32_t* bt = block_tables + (size_t)seg * max_blocks;
-    const size_t page_stride = (size_t)nkv * page_size * (HD + VD);
-    const size_t v_base = (size_t)nkv * page_size * HD;       // where a page's values begin
+    // v_in_key: a key's first VD values are its value (a page holds the keys alone)
+    const size_t page_stride = (size_t)nkv * page_size * (v_in_key ? HD : HD + VD);
+    const size_t v_base = v_in_key ? 0 : (size_t)nkv * page_size * HD;       // where a page's values begin
+    const int v_stride = v_in_key ? HD : VD;
 
     // with a bias the scores are turned into base-2 exponents (scale, bias and log2 e) before the maximum is taken
     const float score_log2 = scale * 1.4426950408889634f;
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
             if (key <= last_pos && key >= lo_first) {
                 const T* pg = cache + (size_t)bt[key / page_size] * page_stride;
                 const size_t in_page = (size_t)kvh * page_size + key % page_size;
-                cp_async16(dst, c < CHUNKS ? pg + in_page * HD + c * 8 : pg + v_base + in_page * VD + (c - CHUNKS) * 8);
+                cp_async16(dst, c < CHUNKS ? pg + in_page * HD + c * 8 : pg + v_base + in_page * v_stride + (c - CHUNKS) * 8);
             } else {                                // never read as a key (masked), but keep the values finite
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
@@ -321,7 +323,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2) attention_prefill_kernel(
 template <int HD, int VD>
 static int launch_prefill(const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
                           int nkv, int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist,
-                          cudaStream_t stream) {
+                          int v_in_key, cudaStream_t stream) {
     constexpr int LD = HD + 8, LDV = VD + 8;
     size_t smem = (size_t)(PF_BM * LD + 4 * PF_BN * (LD + LDV)) * 2 + 4 * 128 * sizeof(float);
     const size_t hand = (size_t)(PF_BM * LD + 2 * PF_BN * (LD + LDV)) * 2 + (size_t)PF_GROUP * (VD / 8 * 4 + 4) * sizeof(float);
@@ -333,14 +335,14 @@ static int launch_prefill(const void* q, const void* cache, const int32_t* bt, c
     }
     dim3 grid(n_tiles, nh);
     return launch_plain(kern, grid, dim3(PF_THREADS), smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt, tiles,
-                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist);
+                            (__nv_bfloat16*)out, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key);
 }
 
 template <int HD>
 static int launch_prefill_v(int vd, const void* q, const void* cache, const int32_t* bt, const int32_t* tiles, void* out, int n_tiles, int nh,
                             int nkv, int page_size, int max_blocks, float scale, int window, const float* dist_bias, int max_dist,
-                            cudaStream_t stream) {
-#define GO(VD) return launch_prefill<HD, VD>(q, cache, bt, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, stream)
+                            int v_in_key, cudaStream_t stream) {
+#define GO(VD) return launch_prefill<HD, VD>(q, cache, bt, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, stream)
     switch (vd) {
         case 32: GO(32);
         case 64: GO(64);
@@ -364,7 +366,7 @@ VK_API int vk_attention_prefill(const void* q, const void* cache, const int32_t*
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0) return VK_BAD_SHAPE;
     if (nh > 65535) return VK_TOO_LARGE;
     if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
-#define GO(HD) return launch_prefill<HD, HD>(q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, nullptr, 0, stream)
+#define GO(HD) return launch_prefill<HD, HD>(q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, nullptr, 0, 0, stream)
     switch (hd) {
         case 16: GO(16);
         case 32: GO(32);
@@ -378,14 +380,16 @@ VK_API int vk_attention_prefill(const void* q, const void* cache, const int32_t*
 
 // The same for the unrotated form of the attention: values of size vd (out [all tokens, nh*vd]; a page holds its keys, then
 // its values) and an optional bias by distance.  Head sizes 32, 64, 96 and 128 for keys and for values, in any pairing.
+// v_in_key: the cache holds keys alone and a key's first vd values are its value (vd <= hd).
 VK_API int vk_attention_prefill_biased(const void* q, const void* cache, const int32_t* block_tables, const int32_t* tiles, void* out,
                                        int n_tiles, int nh, int nkv, int hd, int vd, int page_size, int max_blocks, float scale, int window,
-                                       const float* dist_bias, int max_dist, cudaStream_t stream) {
+                                       const float* dist_bias, int max_dist, int v_in_key, cudaStream_t stream) {
     if (n_tiles <= 0) return VK_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || page_size <= 0 || max_blocks <= 0 || window < 0 || (dist_bias && max_dist <= 0)) return VK_BAD_SHAPE;
+    if (v_in_key && vd > hd) return VK_BAD_SHAPE;
     if (nh > 65535) return VK_TOO_LARGE;
     if (((uintptr_t)q % 16) || ((uintptr_t)cache % 16) || ((uintptr_t)out % 4)) return VK_BAD_ALIGNMENT;
-#define GO(HD) return launch_prefill_v<HD>(vd, q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, stream)
+#define GO(HD) return launch_prefill_v<HD>(vd, q, cache, block_tables, tiles, out, n_tiles, nh, nkv, page_size, max_blocks, scale, window, dist_bias, max_dist, v_in_key, stream)
     switch (hd) {
         case 32: GO(32);
         case 64: GO(64);

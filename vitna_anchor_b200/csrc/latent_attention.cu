@@ -5,8 +5,8 @@
 // and values' expansions folded into the neighbouring matrices, a head's query is  [ W_uk^T q_plain | rot(q_rot) ]
 // (kv_rank + rot_dim values), its score against a cached row their dot product, and its output the weighted sum of the
 // rows' c, which the folded output matrix takes on.  So the attention is one with a single key-value head whose key is the
-// row and whose value is the row's first kv_rank values.  A page of the cache layer is [page_size][kv_rank + rot_dim] keys
-// followed by [page_size][kv_rank] values (c once more, where the attention kernels expect values).
+// row and whose value is the row's first kv_rank values (the attention kernels' "value inside the key" form).  A page of
+// the cache layer is [page_size][kv_rank + rot_dim].
 //
 //  latent_prepare   one block a token, from the float32 row of the first product [ cq_raw | c_raw, kr_raw | ... ]:
 //                   cq = cq_raw / rms * w  to the compute dtype;  c = c_raw / rms * w  and  kr = rot(kr_raw, position)  into the
@@ -52,16 +52,8 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)kv_rank + eps);
     const int hd = kv_rank + rot_dim;
-    const size_t page_stride = (size_t)page_size * (hd + kv_rank);
-    T* page = cache + (size_t)(s / page_size) * page_stride;
-    const int off = s % page_size;
-    T* krow = page + (size_t)off * hd;
-    T* vrow = page + (size_t)page_size * hd + (size_t)off * kv_rank;
-    for (int i = tid; i < kv_rank; i += blockDim.x) {
-        const T c = from_f32<T>((kv[i] * inv) * kvn_w[i]);
-        krow[i] = c;
-        vrow[i] = c;
-    }
+    T* krow = cache + (size_t)s * hd;                        // a page is [page_size][hd]: slot s is row s of the layer
+    for (int i = tid; i < kv_rank; i += blockDim.x) krow[i] = from_f32<T>((kv[i] * inv) * kvn_w[i]);
     const float* kr = kv + kv_rank;
     const float pos = (float)positions[t];
     for (int i = tid; i < dims / 2; i += blockDim.x) {

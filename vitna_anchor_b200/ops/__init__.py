@@ -786,13 +786,15 @@ def qk_norm_store(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
 
 def attention_rows_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
                           positions: torch.Tensor, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float,
-                          window: int = 0, dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          window: int = 0, dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None,
+                          v_in_key: bool = False) -> torch.Tensor:
     """Causal attention of every token (or of those in tok_list) over its request's pages, any sizes, float32 arithmetic,
-    with values of size vd and, if given, dist_bias [distances, nh] (float32) added to the scaled scores by min(distance, last row)."""
+    with values of size vd and, if given, dist_bias [distances, nh] (float32) added to the scaled scores by min(distance, last row).
+    v_in_key: the cache holds keys alone and a key's first vd values are its value."""
     _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
     _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
     T = q.shape[0]
-    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd) != page_size:
         raise KernelError("attention_rows_biased: shapes do not fit the head counts")
     if token_seg.shape[0] != T or positions.shape[0] != T:
         raise KernelError("attention_rows_biased: per-token arrays differ in length")
@@ -806,7 +808,8 @@ def attention_rows_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tabl
         n = tok_list.shape[0]
     _check(lib().vk_attention_rows_biased(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out), n, nh,
                                           nkv, hd, vd, page_size, block_tables.shape[1], ctypes.c_float(scale), window, _p(dist_bias),
-                                          0 if dist_bias is None else dist_bias.shape[0], _dt(q), _stream()), "attention_rows_biased")
+                                          0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), _dt(q), _stream()),
+           "attention_rows_biased")
     return out
 
 
@@ -888,14 +891,15 @@ def delta_rule(proj: torch.Tensor, conv_w: torch.Tensor, a_log: torch.Tensor, dt
 def attention_decode_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, token_seg: torch.Tensor,
                             positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, scratch_tokens: int, nh: int, nkv: int, hd: int,
                             vd: int, page_size: int, scale: float, max_context: int, grid_context: int, window: int = 0,
-                            dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            dist_bias: Optional[torch.Tensor] = None, tok_list: Optional[torch.Tensor] = None,
+                            v_in_key: bool = False) -> torch.Tensor:
     """The split-key attention of single decoded tokens in the unrotated form: values of size vd, an optional bias by distance.
     scratch: attention_decode_scratch_bytes(scratch_tokens, nh, nkv, max(hd, vd), max_context) bytes, zero at first use."""
     _req(q, "q", dims=2); _req(cache_layer, "cache_layer", q.dtype); _req(block_tables, "block_tables", torch.int32, 2)
     _req(token_seg, "token_seg", torch.int32, 1); _req(positions, "positions", torch.int32, 1); _req(out, "out", q.dtype, 2)
     _req(scratch, "scratch", torch.uint8, 1)
     T = q.shape[0]
-    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size:
+    if q.shape[1] != nh * hd or out.shape != (T, nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd) != page_size:
         raise KernelError("attention_decode_biased: shapes do not fit the head counts")
     if dist_bias is not None:
         _req(dist_bias, "dist_bias", torch.float32, 2)
@@ -910,7 +914,8 @@ def attention_decode_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
     _check(lib().vk_attention_decode_biased(_p(q), _p(cache_layer), _p(block_tables), _p(token_seg), _p(positions), _p(tok_list), _p(out),
                                             _p(scratch), scratch_tokens, n, nh, nkv, hd, vd, page_size, block_tables.shape[1], max_context,
                                             grid_context, ctypes.c_float(scale), window, _p(dist_bias),
-                                            0 if dist_bias is None else dist_bias.shape[0], _dt(q), _stream()), "attention_decode_biased")
+                                            0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), _dt(q), _stream()),
+           "attention_decode_biased")
     return out
 
 
@@ -919,12 +924,12 @@ BIASED_PREFILL_HEAD_SIZES = (32, 64, 96, 128)
 
 def attention_prefill_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, out: torch.Tensor,
                              nh: int, nkv: int, hd: int, vd: int, page_size: int, scale: float, window: int = 0,
-                             dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                             dist_bias: Optional[torch.Tensor] = None, v_in_key: bool = False) -> torch.Tensor:
     """Causal attention of prompt portions in bfloat16 on the tensor cores, in the unrotated form.  tiles int32 [n, 4]: first
     token, rows (1..64), position of the first token, segment."""
     _req(q, "q", torch.bfloat16, 2); _req(cache_layer, "cache_layer", torch.bfloat16)
     _req(block_tables, "block_tables", torch.int32, 2); _req(tiles, "tiles", torch.int32, 2); _req(out, "out", torch.bfloat16, 2)
-    if (q.shape[1] != nh * hd or out.shape != (q.shape[0], nh * vd) or _page_size_of(cache_layer, nkv, hd, vd) != page_size
+    if (q.shape[1] != nh * hd or out.shape != (q.shape[0], nh * vd) or _page_size_of(cache_layer, nkv, hd, 0 if v_in_key else vd) != page_size
             or tiles.shape[1] != 4):
         raise KernelError("attention_prefill_biased: shapes do not fit the head counts")
     if hd not in BIASED_PREFILL_HEAD_SIZES or vd not in BIASED_PREFILL_HEAD_SIZES:
@@ -935,14 +940,15 @@ def attention_prefill_biased(q: torch.Tensor, cache_layer: torch.Tensor, block_t
             raise KernelError("attention_prefill_biased: the bias table is not [distances, heads]")
     _check(lib().vk_attention_prefill_biased(_p(q), _p(cache_layer), _p(block_tables), _p(tiles), _p(out), tiles.shape[0], nh, nkv, hd, vd,
                                              page_size, block_tables.shape[1], ctypes.c_float(scale), window, _p(dist_bias),
-                                             0 if dist_bias is None else dist_bias.shape[0], _stream()), "attention_prefill_biased")
+                                             0 if dist_bias is None else dist_bias.shape[0], int(v_in_key), _stream()), "attention_prefill_biased")
     return out
 
 
 def attention_biased(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch.Tensor, nh: int, nkv: int, hd: int, vd: int,
-                     page_size: int, scale: float, window: int = 0, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal attention of a mixed batch over the paged cache in the unrotated form (values of their own size, a bias by
-    distance); `meta` is the page group's GroupMeta.  Single decoded tokens take the split-key kernel, tokens of prompt
+                     page_size: int, scale: float, window: int = 0, dist_bias: Optional[torch.Tensor] = None,
+                     v_in_key: bool = False) -> torch.Tensor:
+    """Causal attention of a mixed batch over the paged cache in the unrotated form (values of their own size, or the
+    first vd values of the keys with v_in_key; a bias by distance); `meta` is the page group's GroupMeta.  Single decoded tokens take the split-key kernel, tokens of prompt
     portions the tensor-core kernel (bfloat16, head sizes it is built for); whatever is left, and the whole exact 32-bit
     routing, takes attention_rows_biased, which takes every size."""
     vec = 4 if q.dtype == torch.float32 else 8
@@ -952,16 +958,16 @@ def attention_biased(q: torch.Tensor, pages: torch.Tensor, meta, ctx, out: torch
     pre_ok = (bool(ctx.num_pre) and q.dtype == torch.bfloat16 and hd in BIASED_PREFILL_HEAD_SIZES and vd in BIASED_PREFILL_HEAD_SIZES
               and ctx.pre_tiles is not None and q.data_ptr() % 16 == 0 and pages.data_ptr() % 16 == 0)
     rows = lambda toks: attention_rows_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, nh, nkv, hd, vd, page_size,
-                                              scale, window, dist_bias, toks)
+                                              scale, window, dist_bias, toks, v_in_key)
     if dec_ok:
         ws = ctx.workspace
         cap, layout = ws.max_segments, ws.max_context
         nbytes = attention_decode_scratch_bytes(cap, nh, nkv, max(hd, vd), layout)
         scratch = ws.flat(f"att.decb/{nh}/{nkv}/{hd}/{vd}/{layout}", nbytes, torch.uint8, zero=True)
         attention_decode_biased(q, pages, meta.block_tables, ctx.token_seg, ctx.positions, out, scratch, cap, nh, nkv, hd, vd, page_size,
-                                scale, layout, min(layout, max(1, ctx.max_context)), window, dist_bias, ctx.dec_tokens)
+                                scale, layout, min(layout, max(1, ctx.max_context)), window, dist_bias, ctx.dec_tokens, v_in_key)
     if pre_ok:
-        attention_prefill_biased(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, vd, page_size, scale, window, dist_bias)
+        attention_prefill_biased(q, pages, meta.block_tables, ctx.pre_tiles, out, nh, nkv, hd, vd, page_size, scale, window, dist_bias, v_in_key)
     if not dec_ok and not pre_ok:
         return rows(None)
     if ctx.num_pre and not pre_ok:
@@ -1045,7 +1051,7 @@ def latent_prepare(proj: torch.Tensor, q_rank: int, q_norm_w: torch.Tensor, cq: 
                    cache_layer: Optional[torch.Tensor] = None, page_size: int = 0) -> torch.Tensor:
     """From the float32 rows of the first product: the normed query latent to cq (compute dtype) and, with kv_off >= 0 and a
     cache layer, the normed key-value latent and the rotated shared key part into the tokens' cache slots
-    (a page: [page_size][kv_rank + rot_dim] keys, then [page_size][kv_rank] values)."""
+    (a page: [page_size][kv_rank + rot_dim]; the row's first kv_rank values are read as the value too)."""
     _req(proj, "proj", torch.float32, 2); _req(q_norm_w, "q_norm_w", torch.float32, 1); _req(cq, "cq", dims=2)
     _req(positions, "positions", torch.int32, 1); _req(freq, "freq", torch.float32, 1)
     T, N = proj.shape
@@ -1056,7 +1062,7 @@ def latent_prepare(proj: torch.Tensor, q_rank: int, q_norm_w: torch.Tensor, cq: 
         _req(kv_norm_w, "kv_norm_w", torch.float32, 1); _req(slot_mapping, "slot_mapping", torch.int32, 1)
         _req(cache_layer, "cache_layer", cq.dtype)
         if (kv_norm_w.shape[0] != kv_rank or slot_mapping.shape[0] < T
-                or _page_size_of(cache_layer, 1, kv_rank + rot_dim, kv_rank) != page_size):
+                or _page_size_of(cache_layer, 1, kv_rank + rot_dim, 0) != page_size):
             raise KernelError("latent_prepare: the cache layer does not fit the latent's sizes")
     _check(lib().vk_latent_prepare(_p(proj), N, q_rank, _p(q_norm_w), _p(cq), kv_off if write else -1, kv_rank, rot_dim,
                                    _p(kv_norm_w if write else None), ctypes.c_float(eps), _p(positions), _p(freq), ctypes.c_float(mag), dims,

@@ -12,8 +12,9 @@ The cache keeps one row [c | kr] a token.  The keys' and values' expansions are 
 load, in float64:  q_plain . (W_uk c) = (W_uk^T q_plain) . c,  so the query product is made with the rows
 [W_uk_h^T W_uq_h,plain ; W_uq_h,rot] per head and gives [kv_rank + rot_dim] values a head that are dotted with the cached
 row as it is; and  W_o,h (W_uv_h sum_j p_j c_j)  is made with W_o,h W_uv_h  on the weighted sum of the rows' c.  What runs is
-an attention with ONE key-value head of size kv_rank + rot_dim and values of size kv_rank (the framework's kernels for
-values of their own size), between two ordinary products.  A layer may read the rows that another layer wrote
+an attention with ONE key-value head of size kv_rank + rot_dim whose values are the keys' first kv_rank values (the
+framework's kernels for values of their own size, reading them inside the key rows, so that c is cached once), between
+two ordinary products.  A layer may read the rows that another layer wrote
 (`shares_kv`: it has no W_dkv of its own; its run names the other layer's cache and does not write it).
 
 The first product stacks W_dq, W_dkv and W_g and leaves float32; both RMS norms, the rotation's angles (float32 position
@@ -83,7 +84,7 @@ class LatentAttention(Mixer):
         return [self.w_in, self.w_q, self.w_out, self.q_norm] + ([] if self.kv_norm is None else [self.kv_norm])
 
     def cache_spec(self):
-        return KVSpec(1, self.kv_rank + self.rot_dim, 0, self.kv_rank)
+        return KVSpec(1, self.kv_rank + self.rot_dim, 0, self.kv_rank, value_in_key=True)
 
     def forward(self, xn: torch.Tensor, ctx: StepContext, cache: LayerCacheView, residual: torch.Tensor, write_cache: bool = True,
                 norm=None) -> None:
@@ -92,7 +93,7 @@ class LatentAttention(Mixer):
         T, ws, H = ctx.num_tokens, ctx.workspace, self.H
         hd = self.kv_rank + self.rot_dim
         meta = ctx.groups[cache.group]
-        ps = ops._page_size_of(cache.pages, 1, hd, self.kv_rank)
+        ps = ops._page_size_of(cache.pages, 1, hd, 0)
         proj = ops.linear(xn, self.w_in, ws.rows("lat.proj", T, self.w_in.shape[0], torch.float32), ops.LINEAR_F32)
         cq = ops.latent_prepare(proj, self.q_rank, self.q_norm, ws.rows("lat.cq", T, self.q_rank, ctx.dtype), self.eps, ctx.positions,
                                 self.freq, self.mag, self.rot_dims, self.interleaved, kv_off=self.kv_off, kv_rank=self.kv_rank,
@@ -101,7 +102,7 @@ class LatentAttention(Mixer):
         q = ops.linear(cq, self.w_q, ws.rows("lat.q", T, H * hd, ctx.dtype), ops.LINEAR_SAME)
         ops.latent_rotate_q(q, ctx.positions, self.freq, self.mag, H, self.kv_rank, self.rot_dim, self.rot_dims, self.interleaved)
         att = ops.attention_biased(q, cache.pages, meta, ctx, ws.rows("lat.out", T, H * self.kv_rank, ctx.dtype), H, 1, hd, self.kv_rank, ps,
-                                   self.scale, 0, None)
+                                   self.scale, 0, None, v_in_key=True)
         if self.gated:
             ops.head_gate(att, proj, self.gate_off, H)
         ops.linear(att, self.w_out, residual, ops.LINEAR_ACC_F32)
